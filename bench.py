@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path: decode dequant-matvec HBM GB/s (headline), with the
+prefill dequant-GEMM TFLOP/s reported beside it.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (one process per GPU under torchrun)
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU algorithm on the host cores
+
+Workload (N = 1): the 4-bit group-64 matvec of the bit-width x group sweep, W out=11008 x in=4096, M = 1,
+fp16 activations, fp32 output.  One step = one pass over LAYERS distinct weight sets (LAYERS x 25.4 MB =
+406 MB, larger than the 126 MB L2, so every launch streams its weights from HBM), i.e. LAYERS launches.
+value = algorithmic bytes (packed codes + scales + biases + x + y) per second.
+
+N > 1 (weak scaling): every rank holds its own 11008-row shard of a (N x 11008)-row projection; a step
+is the same pass, each launch followed by the all-gather of the fp32 output slices over NVLink.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+O_ROWS, K_COLS, BITS, GS = 11008, 4096, 4, 64
+LAYERS = 16
+METRIC = "decode_qmv_hbm_gbs"
+UNIT = "GB/s"
+
+
+def alg_bytes(O, K, bits, gs, M, s_size=2, x_size=2, y_size=4):
+    """Algorithmic bytes of one call: packed codes + scales + biases + activations + outputs."""
+    return O * K * bits // 8 + 2 * O * (K // gs) * s_size + M * K * x_size + M * O * y_size
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained":
+                d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(seconds_target: float = 12.0):
+    """The oracle's restatement of the reference's CPU path (unpack + fp32 dequant + fp32 dot, OpenMP over
+    output rows) timed on the host cores, on one 11008 x 4096 layer of the same workload."""
+    from oracle import oracle
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    lay = synth.make_layer(O_ROWS, K_COLS, BITS, GS, synth.F16, seed=0, keep_codes=False)
+    _, x = synth.make_activations(1, K_COLS, synth.F16, seed=1)
+    cores = len(os.sched_getaffinity(0))
+    packed8 = lay.packed.view(np.uint8)
+    call = lambda: oracle.qmatmul(packed8, lay.scales_raw, lay.biases_raw, lay.scale_dtype, x, K_COLS, BITS, GS,
+                                  accumulate_double=False, threads=cores)
+    call()
+    t0 = time.perf_counter()
+    call()
+    one = time.perf_counter() - t0
+    reps = max(3, min(200, int(seconds_target / max(one, 1e-4))))
+    best = one
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        call()
+        best = min(best, time.perf_counter() - t0)
+    gbs = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1) / best / 1e9
+    return {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"one {O_ROWS}x{K_COLS} 4-bit g64 layer, M=1, best of {reps + 1} calls, fp32 accumulate",
+            "ms_per_call": best * 1e3}
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU algorithm (oracle port; the Swift sources cannot be built on
+    Linux) on all host cores.  A step is one matvec over one layer of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    lay = synth.make_layer(O_ROWS, K_COLS, BITS, GS, synth.F16, seed=0, keep_codes=False)
+    _, x = synth.make_activations(1, K_COLS, synth.F16, seed=1)
+    cores = len(os.sched_getaffinity(0))
+    packed8 = lay.packed.view(np.uint8)
+    call = lambda: oracle.qmatmul(packed8, lay.scales_raw, lay.biases_raw, lay.scale_dtype, x, K_COLS, BITS, GS,
+                                  accumulate_double=False, threads=cores)
+    for _ in range(max(args.warmup, 1)):
+        call()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        call()
+    dt = time.perf_counter() - t0
+    gbs = args.steps * alg_bytes(O_ROWS, K_COLS, BITS, GS, 1) / dt / 1e9
+    sample = f"one {O_ROWS}x{K_COLS} 4-bit g64 layer per step, M=1, fp32 accumulate, OpenMP over rows"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1 (CPU, one layer per step)"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def prefill_probe(mlxq, torch, device, peaks):
+    """The prefill dequant-GEMM beside the headline: 14336 x 4096, 4-bit g64, bf16 in/out, M = 2048."""
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    O, K, M = 14336, 4096, 2048
+    try:
+        lay = synth.make_layer(O, K, 4, 64, synth.BF16, seed=3, keep_codes=False)
+        w = torch.from_numpy(lay.packed.view(np.int32)).to(device)
+        s = torch.from_numpy(lay.scales_raw.view(np.int16)).to(device).view(torch.bfloat16)
+        b = torch.from_numpy(lay.biases_raw.view(np.int16)).to(device).view(torch.bfloat16)
+        lin = mlxq.Linear(w, s, b, None, inDim=K, name="prefill")
+        if lin.kernelFor(M, mlxq.BF16, mlxq.BF16) != "qgemm":
+            return {"available": False}
+        x = torch.randn((M, K), device=device, dtype=torch.bfloat16)
+        ys = [torch.empty((M, O), device=device, dtype=torch.bfloat16) for _ in range(2)]
+        for i in range(3):
+            lin.encode(None, x, K, ys[i % 2], O, M)
+        torch.cuda.synchronize()
+        reps = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            lin.encode(None, x, K, ys[i % 2], O, M)
+        e1.record()
+        torch.cuda.synchronize()
+        mlxq.streamStatus(None, device.index or 0)
+        ms = e0.elapsed_time(e1) / reps
+        tf = 2.0 * M * O * K / (ms * 1e-3) / 1e12
+        return {"available": True, "workload": f"prefill GEMM {O}x{K} b4 g64 M={M} bf16", "tflops": tf, "ms": ms,
+                "frac_of_burst_peak": tf / peaks["bf16_tflops"], "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"]}
+    except Exception as e:      # the probe must never take the headline down
+        return {"available": False, "error": str(e)[:200]}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    mlxq = importlib.import_module("mlx-runner_b200")
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    comm = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="nccl", device_id=device)
+        idt = torch.zeros(128, dtype=torch.uint8, device=device)
+        if rank == 0:
+            idt.copy_(torch.tensor(list(mlxq.Comm.uniqueId()), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        comm = mlxq.Comm(rank, world, local, bytes(idt.cpu().tolist()))
+    peaks = measured_peaks()
+
+    # LAYERS distinct weight sets on this rank (its shard of each layer when world > 1).
+    layers, keep = [], []
+    for i in range(LAYERS):
+        lay = synth.make_layer(O_ROWS, K_COLS, BITS, GS, synth.F16, seed=1000 * rank + i, keep_codes=False)
+        w = torch.from_numpy(lay.packed.view(np.int32)).to(device)
+        s = torch.from_numpy(lay.scales_raw.view(np.int16)).to(device).view(torch.float16)
+        b = torch.from_numpy(lay.biases_raw.view(np.int16)).to(device).view(torch.float16)
+        keep.append((w, s, b))
+        if world > 1:
+            layers.append(mlxq.Linear.shard(w, s, b, None, inDim=K_COLS, rank=rank, nranks=world, full=False,
+                                            name=f"layer{i}", device=local))
+        else:
+            layers.append(mlxq.Linear(w, s, b, None, inDim=K_COLS, name=f"layer{i}", device=local))
+    total_rows = O_ROWS * world
+    x_raw, _ = synth.make_activations(1, K_COLS, synth.F16, seed=7)
+    x_host = torch.from_numpy(x_raw.view(np.int16)).view(torch.float16).pin_memory()
+    x_dev = x_host.to(device)
+    y_dev = torch.zeros((LAYERS, total_rows), dtype=torch.float32, device=device)
+    y_host = torch.empty((LAYERS, total_rows), dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for i, lin in enumerate(layers):
+            if comm is not None:
+                comm.forwardGather(lin, stream, x_dev, K_COLS, y_dev[i], total_rows, 1)
+            else:
+                lin.encode(stream, x_dev, K_COLS, y_dev[i], O_ROWS, 1)
+
+    def step_e2e():
+        x_dev.copy_(x_host, non_blocking=True)
+        step()
+        y_host.copy_(y_dev, non_blocking=True)
+        stream.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(step, args.steps)
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    mlxq.streamStatus(stream, local)
+
+    per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1)
+    launches = args.steps * LAYERS
+    value = world * launches * per_launch / (ms * 1e-3) / 1e9
+    e2e_value = world * launches * per_launch / (ms_e2e * 1e-3) / 1e9
+    # Roofline of the dominant kernel (the matvec): per-launch algorithmic bytes over the mean launch time
+    # of the timed region (at N > 1 that time includes the gather, so the N = 1 line is the kernel's figure).
+    achieved = per_launch / (ms * 1e-3 / launches) / 1e9
+    out = None
+    if rank == 0:
+        probe = prefill_probe(mlxq, torch, device, peaks) if world == 1 and not args.no_prefill else {"available": False}
+        cpu = cpu_sample(args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1, fp16 x, fp32 y; "
+                                   f"{LAYERS} distinct weight sets per step ({LAYERS * per_launch / 1e6:.0f} MB > L2)",
+                       "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS, "group_size": GS, "batch": 1,
+                       "launches_per_step": LAYERS, "l2": "inputs larger than L2",
+                       "parallelism": f"row-shard x{world} + all-gather" if world > 1 else "single GPU"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
+                    "d2h_bytes_per_step": int(y_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "frac_of_nominal_8000": achieved / 8000.0, "bytes_per_launch": per_launch},
+            "prefill": probe,
+        }
+        if cpu:
+            out["cpu_baseline"] = cpu
+        tp = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tp):
+            try:
+                out["roofline"]["traffic"] = json.load(open(tp)).get("qmv_b4_bytes_per_launch")
+            except Exception:
+                pass
+        print(json.dumps(out), flush=True)
+    if comm is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length (0 = skip)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM probe")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,184 @@
+/*
+ * mlxq.h -- C ABI of libmlxq, a B200 (sm_100a) implementation of the MLX affine quantized-linear layer.
+ *
+ * The library replaces one class of the reference project (BackendStack21/mlx-runner): `Linear`
+ * (Sources/MLXEngine/Transformer.swift:15-345) and the Metal kernels it dispatches
+ * (Sources/MLXEngine/Kernels.swift:26-1023, 2752-2857).  Every entry point below names the reference
+ * interface it stands in for.  All pointers to tensors are CUDA device pointers owned by the caller;
+ * the library borrows them (as the reference borrows `Tensor` views, GPU.swift:145-154) and they must
+ * outlive the handle.  Calls that take a stream only enqueue work and return; nothing throws or aborts
+ * across this boundary: every call returns an `mlxq_status` and the text of the most recent failure on
+ * the calling thread is available from mlxq_last_error().
+ *
+ * Format (normative): weight u32 [out_dim, in_dim*bits/32]; row r is one little-endian bit stream of
+ * in_dim*bits/8 bytes; code k of the row is bits [k*bits, (k+1)*bits) of that stream.  scales and biases
+ * [out_dim, in_dim/group_size] in f32, f16 or bf16 (same type).  w[r,k] = scale*q + bias, y = x . w^T.
+ */
+#ifndef MLXQ_H
+#define MLXQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MLXQ_API __attribute__((visibility("default")))
+#else
+#define MLXQ_API
+#endif
+
+/* Status codes.  INVALID_FILE / UNSUPPORTED / MISSING_TENSOR / OUT_OF_MEMORY / GPU_FAILURE mirror the
+ * cases of `EngineError` a Linear can raise (GPU.swift:4-33). */
+typedef enum mlxq_status {
+    MLXQ_OK = 0,
+    MLXQ_INVALID_FILE = 1,    /* EngineError.invalidFile: shapes that do not describe a layer */
+    MLXQ_UNSUPPORTED = 2,     /* EngineError.unsupported: bits / group size / dtype outside the format */
+    MLXQ_MISSING_TENSOR = 3,  /* EngineError.missingTensor: scales without biases */
+    MLXQ_OUT_OF_MEMORY = 4,   /* EngineError.outOfMemory */
+    MLXQ_GPU_FAILURE = 5,     /* EngineError.gpuFailure: a CUDA call or an earlier kernel failed */
+    MLXQ_INVALID_ARGUMENT = 6,/* a call the reference leaves undefined (null pointer, misaligned x, T < 1) */
+    MLXQ_NCCL_FAILURE = 7,    /* the all-gather of output slices failed */
+    MLXQ_TIMEOUT = 8          /* a bounded device-side wait ran out */
+} mlxq_status;
+
+/* Element types of scales/biases/bias, activations and outputs (DType, GPU.swift:121-142). */
+typedef enum mlxq_dtype { MLXQ_F32 = 0, MLXQ_F16 = 1, MLXQ_BF16 = 2 } mlxq_dtype;
+
+/* Gate activations of the gated epilogue (act_mul, Kernels.swift:124-130). */
+typedef enum mlxq_act { MLXQ_ACT_SILU = 0, MLXQ_ACT_GELU_TANH = 1, MLXQ_ACT_GELU_ERF = 2 } mlxq_act;
+
+typedef struct mlxq_linear* mlxq_linear_t;
+typedef struct mlxq_comm* mlxq_comm_t;
+typedef void* mlxq_stream_t; /* a cudaStream_t; NULL is the legacy default stream */
+
+/* What `Linear.init(weight:scales:biases:bias:inDim:outDim:name:)` receives (Transformer.swift:48).
+ * bits and group size are derived from the shapes exactly as Transformer.swift:68-70 does:
+ * bits = weight_cols*32/in_dim, group_size = in_dim/scales_cols. */
+typedef struct mlxq_linear_desc {
+    const void* weight;      /* u32 [weight_rows, weight_cols] */
+    const void* scales;      /* [scales_rows, scales_cols], may be NULL only together with biases == NULL (error) */
+    const void* biases;      /* [biases_rows, biases_cols] */
+    const void* bias;        /* optional per-output-row bias [bias_len]; NULL if absent */
+    int64_t weight_rows, weight_cols;
+    int64_t scales_rows, scales_cols;
+    int64_t biases_rows, biases_cols;
+    int64_t bias_len;        /* ignored when bias == NULL */
+    int64_t in_dim;
+    int64_t expect_out;      /* `outDim:` argument; 0 = do not check */
+    int32_t scale_dtype;     /* mlxq_dtype of scales and biases */
+    int32_t bias_dtype;      /* mlxq_dtype of bias */
+    int32_t device;          /* CUDA device ordinal the pointers live on */
+    int32_t reserved;
+    const char* name;        /* used in error text only (the reference's `name prefix`); may be NULL */
+} mlxq_linear_desc;
+
+/* ---- library ----------------------------------------------------------------------------------------- */
+
+/* Library version, major*10000 + minor*100 + patch.  No counterpart in the reference. */
+MLXQ_API int mlxq_version(void);
+/* Text of a status code (EngineError.errorDescription, GPU.swift:18-32). */
+MLXQ_API const char* mlxq_status_string(int status);
+/* Message of the most recent failing call on this thread ("" if none). */
+MLXQ_API const char* mlxq_last_error(void);
+
+/* ---- construction: Linear.init, Transformer.swift:48-111 ------------------------------------------- */
+
+/* Validates the description (shape rules of Transformer.swift:52-60, format rules of :68-73) and returns
+ * a handle.  Nothing is copied.  Errors: MLXQ_INVALID_FILE, MLXQ_UNSUPPORTED, MLXQ_MISSING_TENSOR. */
+MLXQ_API int mlxq_linear_create(const mlxq_linear_desc* desc, mlxq_linear_t* out);
+/* The same layer restricted to output rows [rank*out_dim/nranks, (rank+1)*out_dim/nranks): the row
+ * sharding of large projections across GPUs.  `desc` holds either the full tensors (desc_is_full != 0:
+ * the library offsets the pointers, which must then be reachable from `desc->device`) or tensors the
+ * caller already sliced.  out_dim must be divisible by 8*nranks.  No counterpart in the reference
+ * (it is single-GPU); rows are independent there too (permuteRows, Transformer.swift:113-129). */
+MLXQ_API int mlxq_linear_create_shard(const mlxq_linear_desc* desc, int rank, int nranks, int desc_is_full,
+                                      mlxq_linear_t* out);
+MLXQ_API void mlxq_linear_destroy(mlxq_linear_t h);
+
+/* Properties of `Linear` (Transformer.swift:16-23). */
+MLXQ_API int64_t mlxq_linear_in_dim(mlxq_linear_t h);
+MLXQ_API int64_t mlxq_linear_out_dim(mlxq_linear_t h);
+MLXQ_API int mlxq_linear_bits(mlxq_linear_t h);
+MLXQ_API int mlxq_linear_group_size(mlxq_linear_t h);
+/* First global output row of a shard (0 for an unsharded layer). */
+MLXQ_API int64_t mlxq_linear_row_offset(mlxq_linear_t h);
+
+/* ---- encode: Linear.encode, Transformer.swift:272-315 ---------------------------------------------- */
+
+/* y[t, 0:out_dim] = x[t, 0:in_dim] . W^T (+ bias) for t in [0, T).  Strides are in elements.  Picks the
+ * decode matvec for small T and the tensor-core GEMM for long batches, as the reference picks among
+ * qmv/qmvt4/qmvx4/qgemms/qgemm by T.  x rows must start on 16-byte boundaries (the reference's kernels
+ * load float4, Kernels.swift:93); a violation returns MLXQ_INVALID_ARGUMENT instead of faulting. */
+MLXQ_API int mlxq_linear_forward(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, int64_t x_stride,
+                                 void* y, int y_dtype, int64_t y_stride, int64_t T);
+
+/* Linear.encodeFusedDecode, Transformer.swift:206-244: one launch computing the rows [A | B | C] of up
+ * to three layers that satisfy mlxq_fusable(). */
+MLXQ_API int mlxq_fused_forward(const mlxq_linear_t* parts, int n_parts, mlxq_stream_t stream, const void* x,
+                                int x_dtype, int64_t x_stride, void* y, int y_dtype, int64_t y_stride, int64_t T);
+
+/* Linear.encodeGated, Transformer.swift:247-261: y[o] = act(x . W^T + bias)[o] * e[o], one token.
+ * e is fp32 [out_dim]. */
+MLXQ_API int mlxq_linear_forward_gated(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, void* y,
+                                       int y_dtype, const float* e, int act);
+
+/* Linear.encodeLookup (qembed, Kernels.swift:1002-1023): out[t, :] = dequantised row ids[t], fp32
+ * [T, in_dim].  Ids outside [0, out_dim) produce a row of zeros and set the stream's error word
+ * (see mlxq_stream_status) instead of reading out of bounds. */
+MLXQ_API int mlxq_linear_lookup(mlxq_linear_t h, mlxq_stream_t stream, const int32_t* ids, float* out, int64_t T);
+
+/* The row-list matvec of head_exact (Kernels.swift:2752-2787): y[list[i]] = W[list[i]] . x for
+ * i < *count (count and list live on the device); rows outside [0, out_dim) are skipped. */
+MLXQ_API int mlxq_linear_forward_rows(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, float* y,
+                                      const uint32_t* count, const int32_t* list, int64_t max_rows);
+
+/* Writes the codes of every weight as one byte each, u8 [out_dim, in_dim].  The GPU half of the
+ * bit-exact unpack check (unpack8, Kernels.swift:34-55). */
+MLXQ_API int mlxq_unpack_codes(mlxq_linear_t h, mlxq_stream_t stream, uint8_t* out);
+
+/* ---- host policy the reference's tests pin ---------------------------------------------------------- */
+
+/* Linear.fusable, Transformer.swift:191-198. */
+MLXQ_API int mlxq_fusable(const mlxq_linear_t* parts, int n_parts);
+/* Linear.canFuse, Transformer.swift:201-203. */
+MLXQ_API int mlxq_can_fuse(const mlxq_linear_t* parts, int n_parts, int64_t T);
+/* Linear.useGemm64, Transformer.swift:266-269 (kept as the reference's tile policy; this library's GEMM
+ * picks its own tile with mlxq_gemm_tile_tokens()). */
+MLXQ_API int mlxq_use_gemm64(int64_t T, int64_t out_dim);
+/* Token-tile width the tensor-core GEMM uses for a batch of T tokens (0 = the batch takes the matvec). */
+MLXQ_API int mlxq_gemm_tile_tokens(mlxq_linear_t h, int64_t T);
+/* Name of the kernel family mlxq_linear_forward would launch for T tokens with these dtypes
+ * ("qmv", "qmm", "qgemm"); for tests of the selection table (Transformer.swift:272-315). */
+MLXQ_API const char* mlxq_kernel_for(mlxq_linear_t h, int x_dtype, int y_dtype, int64_t T);
+
+/* ---- errors raised on the device: cb.error -> EngineError.gpuFailure, Transformer.swift:1159-1163 --- */
+
+/* Waits for `stream` and reports a failed launch/kernel or a device-side error word (bad lookup id,
+ * a bounded wait that ran out) as a status.  Clears the error word. */
+MLXQ_API int mlxq_stream_status(mlxq_stream_t stream, int device);
+
+/* ---- output-row sharding across GPUs (no counterpart in the reference) ----------------------------- */
+
+#define MLXQ_COMM_ID_BYTES 128
+/* Fills `id` with a fresh rendezvous token; rank 0 calls it and hands the bytes to the other ranks. */
+MLXQ_API int mlxq_comm_unique_id(uint8_t id[MLXQ_COMM_ID_BYTES]);
+/* Joins the communicator of `nranks` GPUs (one process per GPU) on `device`. */
+MLXQ_API int mlxq_comm_create(const uint8_t id[MLXQ_COMM_ID_BYTES], int rank, int nranks, int device,
+                              mlxq_comm_t* out);
+MLXQ_API void mlxq_comm_destroy(mlxq_comm_t c);
+MLXQ_API int mlxq_comm_rank(mlxq_comm_t c);
+MLXQ_API int mlxq_comm_size(mlxq_comm_t c);
+/* Shard forward + all-gather: computes this rank's rows into y[t, row_offset : row_offset+rows] and
+ * all-gathers the slices so every rank holds y[T, out_dim_total] (fp32, row stride y_stride).  `h` must
+ * come from mlxq_linear_create_shard with the communicator's rank and size.  With one rank no
+ * collective is issued. */
+MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t stream, const void* x,
+                                        int x_dtype, int64_t x_stride, float* y, int64_t y_stride, int64_t T);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLXQ_H */

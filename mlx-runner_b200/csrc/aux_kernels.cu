@@ -1,0 +1,113 @@
+// Small kernels beside the matvec / GEMM: code unpack (the bit-exact format check), embedding-row lookup
+// and the row-list matvec.  All three walk the bit stream in 8-code chunks (BITS bytes each, byte
+// aligned for every bit width).
+#include "aux_kernels.cuh"
+
+namespace mlxq {
+
+// out[r, k] = code k of row r, one byte each.  One thread per 8-code chunk.
+__global__ void unpack_codes_kernel(const uint8_t* __restrict__ w, uint8_t* __restrict__ out, long long rows, int K,
+                                    int bits) {
+    const long long chunks_per_row = K / 8;
+    const long long n = rows * chunks_per_row;
+    const unsigned mask = (1u << bits) - 1u;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / chunks_per_row, c = i - r * chunks_per_row;
+        const uint64_t v = chunk_bits_rt(w + (static_cast<size_t>(r) * K / 8 + c) * bits, bits);
+        uint64_t packed = 0;
+        for (int j = 0; j < 8; j++) packed |= static_cast<uint64_t>((v >> (j * bits)) & mask) << (8 * j);
+        *reinterpret_cast<uint64_t*>(out + static_cast<size_t>(r) * K + c * 8) = packed;
+    }
+}
+
+// out[t, k] = scale * q[ids[t], k] + bias, fp32.  Grid (chunks, T).
+__global__ void lookup_kernel(const uint8_t* __restrict__ w, const void* __restrict__ scales, const void* __restrict__ biases,
+                              int s_dtype, const int32_t* __restrict__ ids, float* __restrict__ out, int rows, int K, int gs,
+                              int bits, unsigned* err) {
+    const int t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= K / 8) return;
+    const int row = __ldg(ids + t);
+    float* o = out + static_cast<size_t>(t) * K + c * 8;
+    if (row < 0 || row >= rows) {
+        if (c == 0) atomicOr(err, ERR_BAD_LOOKUP_ID);
+        for (int j = 0; j < 8; j++) o[j] = 0.0f;
+        return;
+    }
+    const size_t row_bytes = static_cast<size_t>(K) * bits / 8;
+    const uint64_t v = chunk_bits_rt(w + row * row_bytes + static_cast<size_t>(c) * bits, bits);
+    const unsigned mask = (1u << bits) - 1u;
+    const size_t gi = static_cast<size_t>(row) * (K / gs) + (c * 8) / gs;
+    const float s = load_scalar(scales, s_dtype, gi), b = load_scalar(biases, s_dtype, gi);
+    for (int j = 0; j < 8; j++) {
+        // multiply then add, two roundings: the layer's definition evaluates q*scale + bias unfused
+        o[j] = __fadd_rn(__fmul_rn(static_cast<float>((v >> (j * bits)) & mask), s), b);
+    }
+}
+
+// y[list[i]] = W[list[i]] . x for i < *count, one warp per listed row.
+__global__ void rows_kernel(const uint8_t* __restrict__ w, const void* __restrict__ scales, const void* __restrict__ biases,
+                            int s_dtype, const void* __restrict__ x, int x_dtype, float* __restrict__ y,
+                            const uint32_t* __restrict__ count, const int32_t* __restrict__ list, int rows, int K, int gs,
+                            int bits) {
+    const unsigned e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (e >= __ldg(count)) return;
+    const int row = __ldg(list + e);
+    if (row < 0 || row >= rows) return;
+    const size_t row_bytes = static_cast<size_t>(K) * bits / 8;
+    const uint8_t* wr = w + row * row_bytes;
+    const int gpr = K / gs;
+    const unsigned mask = (1u << bits) - 1u;
+    float acc = 0.0f;
+    for (int c = lane; c < K / 8; c += 32) {
+        const uint64_t v = chunk_bits_rt(wr + static_cast<size_t>(c) * bits, bits);
+        float d = 0.0f, xs = 0.0f;
+        for (int j = 0; j < 8; j++) {
+            const float xv = load_scalar(x, x_dtype, c * 8 + j);
+            d = fmaf(static_cast<float>((v >> (j * bits)) & mask), xv, d);
+            xs += xv;
+        }
+        const size_t gi = static_cast<size_t>(row) * gpr + (c * 8) / gs;
+        acc = fmaf(load_scalar(biases, s_dtype, gi), xs, fmaf(load_scalar(scales, s_dtype, gi), d, acc));
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if (lane == 0) y[row] = acc;
+}
+
+cudaError_t launch_unpack_codes(const uint8_t* w, uint8_t* out, long long rows, int K, int bits, cudaStream_t st) {
+    const long long n = rows * (K / 8);
+    if (n == 0) return cudaSuccess;
+    const int block = 256;
+    const long long want = (n + block - 1) / block;
+    const unsigned grid = static_cast<unsigned>(want < 148LL * 16 ? want : 148LL * 16);
+    unpack_codes_kernel<<<grid, block, 0, st>>>(w, out, rows, K, bits);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_lookup(const uint8_t* w, const void* scales, const void* biases, int s_dtype, const int32_t* ids,
+                          float* out, long long T, int rows, int K, int gs, int bits, unsigned* err, cudaStream_t st) {
+    if (T == 0) return cudaSuccess;
+    const int chunks = K / 8;
+    const int block = chunks < 256 ? ((chunks + 31) / 32) * 32 : 256;
+    // gridDim.y is limited to 65535: walk longer id lists in slices.
+    for (long long t0 = 0; t0 < T; t0 += 65535) {
+        const unsigned ty = static_cast<unsigned>(T - t0 < 65535 ? T - t0 : 65535);
+        lookup_kernel<<<dim3((chunks + block - 1) / block, ty), block, 0, st>>>(
+            w, scales, biases, s_dtype, ids + t0, out + static_cast<size_t>(t0) * K, rows, K, gs, bits, err);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rows(const uint8_t* w, const void* scales, const void* biases, int s_dtype, const void* x, int x_dtype,
+                        float* y, const uint32_t* count, const int32_t* list, long long max_rows, int rows, int K, int gs,
+                        int bits, cudaStream_t st) {
+    if (max_rows == 0) return cudaSuccess;
+    const int warps = 4;
+    rows_kernel<<<static_cast<unsigned>((max_rows + warps - 1) / warps), warps * 32, 0, st>>>(
+        w, scales, biases, s_dtype, x, x_dtype, y, count, list, rows, K, gs, bits);
+    return cudaGetLastError();
+}
+
+}  // namespace mlxq

@@ -1,0 +1,15 @@
+// Launchers of the small kernels beside the matvec / GEMM (see aux_kernels.cu).
+#pragma once
+
+#include "mlxq_device.cuh"
+
+namespace mlxq {
+
+cudaError_t launch_unpack_codes(const uint8_t* w, uint8_t* out, long long rows, int K, int bits, cudaStream_t st);
+cudaError_t launch_lookup(const uint8_t* w, const void* scales, const void* biases, int s_dtype, const int32_t* ids,
+                          float* out, long long T, int rows, int K, int gs, int bits, unsigned* err, cudaStream_t st);
+cudaError_t launch_rows(const uint8_t* w, const void* scales, const void* biases, int s_dtype, const void* x, int x_dtype,
+                        float* y, const uint32_t* count, const int32_t* list, long long max_rows, int rows, int K, int gs,
+                        int bits, cudaStream_t st);
+
+}  // namespace mlxq

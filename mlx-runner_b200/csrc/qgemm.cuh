@@ -1,0 +1,37 @@
+// Interface of the tensor-core dequant-GEMM (qgemm_sm100.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mlxq {
+
+struct GemmLayer {
+    const uint8_t* w;    // packed rows [O, K*bits/8]
+    const void* s;       // scales [O, K/gs]
+    const void* b;       // biases [O, K/gs]
+    const void* bias;    // optional per-row bias [O]
+    int s_dtype, bias_dtype;
+    int O, K, gs, bits;
+    int device;
+};
+
+struct GemmCall {
+    const void* x;       // [T, K], 16-bit elements, row stride x_stride
+    int x_dtype;
+    long long x_stride;
+    void* y;             // [T, O], row stride y_stride
+    int y_dtype;
+    long long y_stride;
+    long long T;
+    unsigned* err;       // device error word
+};
+
+// 0 when the GEMM cannot take this layer / call (the caller then uses the CUDA-core kernel), else the
+// number of tokens per output tile it would use.
+int qgemm_tile_tokens(const GemmLayer& L, int x_dtype, long long x_stride, const void* x, long long T);
+
+// Enqueues the GEMM.  Returns cudaSuccess, or an error with `why` filled in.
+cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why);
+
+}  // namespace mlxq
