@@ -33,7 +33,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 O_ROWS, K_COLS, BITS, GS = 11008, 4096, 4, 64
-LAYERS = 16
+LAYERS = 16          # distinct weight sets per step; --layers overrides it (profiling runs use fewer)
 METRIC = "decode_qmv_hbm_gbs"
 UNIT = "GB/s"
 
@@ -53,46 +53,58 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons through NVML (a read-only query) every few milliseconds while
+    the timed regions run."""
 
     def __init__(self, gpu_index: int):
-        self.rows, self.proc, self.gpu = [], None, gpu_index
+        self.gpu, self.rows, self.stop_flag, self.thread, self.err = gpu_index, [], False, None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.gpu
+            if vis:
+                ent = vis.split(",")[self.gpu].strip()
+                if ent.isdigit():
+                    idx = int(ent)
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.nv = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:      # no NVML: report that instead of a number
+            self.err = str(e)[:100]
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                self.rows.append((time.perf_counter(), float(mhz), int(reasons)))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
-    def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
-        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
-        reasons = set()
-        for r in self.rows:
-            if len(r) < 9:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+    def stop(self, windows=None):
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + str(self.err)]}
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        nv = self.nv
+        rows = self.rows
+        if windows:
+            inside = [r for r in rows if any(a <= r[0] <= b for a, b in windows)]
+            rows = inside or rows
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        seen = sorted(n for n, bit in names.items() if any(r[2] & bit for r in rows))
+        sm = [r[1] for r in rows]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": self.max_mhz, "reasons": seen,
+                "samples": len(sm)}
 
 
 def cpu_sample(seconds_target: float = 12.0):
@@ -188,6 +200,7 @@ def prefill_probe(mlxq, torch, device, peaks):
 
 
 def run_ours(args):
+    LAYERS = args.layers
     import torch
     import torch.distributed as dist
     mlxq = importlib.import_module("mlx-runner_b200")
@@ -266,16 +279,21 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
-    for _ in range(max(args.warmup, 3)):
-        step()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    windows = []
+    t_a = time.perf_counter()
     ms = timed(step, args.steps)
+    windows.append((t_a, time.perf_counter()))
     for _ in range(2):
         step_e2e()
+    t_a = time.perf_counter()
     ms_e2e = timed(step_e2e, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
+    windows.append((t_a, time.perf_counter()))
+    clocks = sampler.stop(windows) if rank == 0 else None
     mlxq.streamStatus(stream, local)
 
     per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1)
@@ -331,6 +349,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length (0 = skip)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM probe")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight sets per step (default 16)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

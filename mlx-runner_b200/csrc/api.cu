@@ -15,6 +15,8 @@
 #include "aux_kernels.cuh"
 #include "qgemm.cuh"
 #include "qmv.cuh"
+#include "qmv_mma.cuh"
+#include "qmv_tma.cuh"
 
 namespace mlxq {
 
@@ -52,6 +54,17 @@ unsigned* device_error_word(int device) {
         if (cur != device) cudaSetDevice(cur);
     }
     return g_err_ptr[device];
+}
+
+int device_sm_count(int device) {
+    static int cached[64] = {};
+    if (device < 0 || device >= 64) return 148;
+    if (!cached[device]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+        cached[device] = n;
+    }
+    return cached[device];
 }
 
 static bool valid_dtype(int dt) { return dt == MLXQ_F32 || dt == MLXQ_F16 || dt == MLXQ_BF16; }
@@ -189,6 +202,23 @@ static void fill_qmv(QmvParams& p, const mlxq_linear_t* parts, int n) {
     for (int s = 3; s < 31; s++) if ((1 << s) == f->gs) p.gs_shift = s;
 }
 
+// The tensor-core decode kernel takes a call when the batch is small, the group size is 32/64/128, K is a
+// multiple of the kernel's step and the rows are aligned for vector loads.  MLXQ_DECODE=cuda forces the
+// CUDA-core kernel (which handles every shape).  Returns the shared memory needed, 0 when not eligible.
+static size_t mma_plan(const mlxq_linear_t* parts, int n, int x_dtype, int64_t T, MmaParams& mp) {
+    const mlxq_linear* f = parts[0];
+    const char* mode = getenv("MLXQ_DECODE");
+    if (mode && strcmp(mode, "cuda") == 0) return 0;
+    if (T > 16 || (f->gs != 32 && f->gs != 64 && f->gs != 128)) return 0;
+    const int kb = qmv_mma_step_codes(f->bits);
+    if (f->in_dim % kb != 0) return 0;
+    for (int i = 0; i < n; i++)
+        if (!aligned16(parts[i]->w)) return 0;
+    mp.split = x_dtype == MLXQ_F32 ? 2 : 1;
+    if (!qmv_mma_plan(f->bits, static_cast<int>(f->in_dim), f->gs, static_cast<int>(T) * mp.split, mp)) return 0;
+    return qmv_mma_smem(static_cast<int>(f->in_dim), f->gs, static_cast<int>(T), mp);
+}
+
 static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const void* x, int x_dtype, int64_t x_stride,
                    void* y, int y_dtype, int64_t y_stride, int64_t T, const float* e, int act) {
     QmvParams p;
@@ -199,6 +229,22 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
     p.y_stride = y_stride;
     p.e = e;
     p.act = act;
+    MmaParams mp;
+    if (const size_t smem = mma_plan(parts, n, x_dtype, T, mp)) {
+        p.T = static_cast<int>(T);
+        p.x = x;
+        p.y = y;
+        mp.q = p;
+        mp.err = device_error_word(parts[0]->device);
+        // Preferred: the persistent kernel fed by TMA bulk copies (MLXQ_DECODE=mma keeps the register-fed one).
+        const char* mode = getenv("MLXQ_DECODE");
+        TmaPlan tp;
+        const size_t tsmem = (mode && strcmp(mode, "mma") == 0) || !mp.err ? 0 : qmv_tma_plan(parts[0]->bits, mp, static_cast<int>(T), tp);
+        cudaError_t err = tsmem ? launch_qmv_tma(parts[0]->bits, mp, tp, tsmem, device_sm_count(parts[0]->device), st)
+                                : launch_qmv_mma(parts[0]->bits, mp, smem, st);
+        if (err != cudaSuccess) return cuda_fail(err, "qmv (tensor-core) launch");
+        return MLXQ_OK;
+    }
     // gridDim.y carries token tiles of four; walk very long batches in slices.
     const int64_t slice = 4 * 65535;
     for (int64_t t0 = 0; t0 < T; t0 += slice) {

@@ -24,6 +24,14 @@ __device__ __forceinline__ float load_scalar(const void* p, int dt, size_t i) {
     return __uint_as_float(static_cast<uint32_t>(u) << 16);
 }
 
+// The same for a shared-memory (or any generic) address: plain loads, no read-only cache hint.
+__device__ __forceinline__ float smem_scalar(const void* p, int dt, size_t i) {
+    if (dt == DT_F32) return reinterpret_cast<const float*>(p)[i];
+    const unsigned short u = reinterpret_cast<const unsigned short*>(p)[i];
+    if (dt == DT_F16) return __half2float(__ushort_as_half(u));
+    return __uint_as_float(static_cast<uint32_t>(u) << 16);
+}
+
 __device__ __forceinline__ void store_scalar(void* p, int dt, size_t i, float v) {
     if (dt == DT_F32) reinterpret_cast<float*>(p)[i] = v;
     else if (dt == DT_F16) reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);

@@ -1,5 +1,418 @@
+// Prefill dequant-GEMM for sm_100a: Y[T, O] = X[T, K] . W[O, K]^T with W in the 4-bit MLX affine format.
+//
+// Mapping onto the 5th-generation tensor cores (tcgen05):
+//   * The weights are the A operand and live in TENSOR MEMORY, not shared memory.  One thread owns one
+//     weight row of the tile: it reads the row's 32 packed bytes of the current 64-wide K slice from shared
+//     memory (staged there by TMA), dequantises them to fp16 (w = scale*q + bias, the group's scale and
+//     bias in registers) and writes the 64 halves to its own TMEM lane with one tcgen05.st.  A in TMEM
+//     needs no swizzled shared-memory tile and costs no shared-memory bandwidth on the MMA side.
+//   * The activations are the B operand: TMA loads [128 tokens x 64] 16-bit tiles with the 128-byte swizzle
+//     and tcgen05.mma reads them through a shared-memory descriptor.  Both operands are fp16: a kind::f16
+//     MMA whose descriptor names fp16 for A and bf16 for B raises an illegal-instruction error on B200, and
+//     bf16 weights would cost 2^-9 per weight, so bf16 activations are first converted to fp16 (exact for
+//     |x| in [6.1e-5, 65504], clamped above) by a small kernel into stream-ordered scratch memory.
+//   * One CTA computes a 256 (rows) x 128 (tokens) output tile as two M=128 MMAs that share every B tile,
+//     accumulating in fp32 in TMEM (2 x 128 columns), K = 16 per instruction, issued by one thread.
+//   * Warp roles: warp 0 TMA producer, warp 1 MMA issuer (and TMEM allocator), warps 2-9 dequantisers
+//     (two warpgroups, one per 128-row half), warps 10-13 epilogue (tcgen05.ld -> row bias -> store).
+//   * Rings: 8 shared-memory stages (24 KB each: X tile + packed W tile) and 4 TMEM stages for A.
+//     All hand-offs are mbarriers; MMA completion is signalled with tcgen05.commit.
+//   * The kernel is persistent: min(#tiles, #SMs) CTAs walk the tile list; row tiles vary fastest so the
+//     CTAs running together share activation tiles in L2.
+// Every wait is bounded: a wait that runs out sets the device error word, raises the CTA's abort flag and
+// all roles fall through to the common exit, where TMEM is released.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "mlxq_device.cuh"
 #include "qgemm.cuh"
+#include "sm100_ptx.cuh"
+
 namespace mlxq {
-int qgemm_tile_tokens(const GemmLayer&, int, long long, const void*, long long) { return 0; }
-cudaError_t launch_qgemm(const GemmLayer&, const GemmCall&, cudaStream_t, const char** why) { *why = "stub"; return cudaErrorNotSupported; }
+
+namespace {
+
+constexpr int BM = 256;                 // weight rows per CTA tile (two M=128 MMA tiles)
+constexpr int BN = 128;                 // tokens per tile
+constexpr int BK = 64;                  // K slice per stage
+constexpr int S_SMEM = 8;               // shared-memory stages
+constexpr int S_A = 4;                  // TMEM stages of the A operand
+constexpr int X_STAGE = BN * BK * 2;    // 16384 bytes
+constexpr int W_STAGE = BM * BK / 2;    // 8192 bytes (4-bit codes)
+constexpr int STAGE_BYTES = X_STAGE + W_STAGE;
+constexpr int NUM_THREADS = 14 * 32;
+constexpr int DEQ_WARP0 = 2, DEQ_WARPS = 8, EPI_WARP0 = 10, EPI_WARPS = 4;
+constexpr int TMEM_COLS = 512;
+constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
+constexpr int A_COL0 = 2 * BN;          // A ring: S_A stages x 2 halves x 32 columns
+
+struct Barriers {
+    uint64_t full_tma[S_SMEM];
+    uint64_t empty_smem[S_SMEM];
+    uint64_t full_a[S_A];
+    uint64_t empty_a[S_A];
+    uint64_t d_full;
+    uint64_t d_empty;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr int SMEM_BYTES = S_SMEM * STAGE_BYTES + sizeof(Barriers) + 1024;   // + alignment slack
+
+struct GemmArgs {
+    const void* s;
+    const void* b;
+    const void* bias;
+    void* y;
+    unsigned* err;
+    long long y_stride;
+    int s_dtype, bias_dtype, y_dtype;
+    int O, K, gs, T;
+    int m_tiles, n_tiles;
+    uint32_t idesc;
+};
+
+// Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128 bytes, 8-row
+// groups 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
+
+__device__ __forceinline__ __half2 scale_pair(const void* p, int dt, size_t i) {
+    return __float2half2_rn(load_scalar(p, dt, i));
+}
+
+// ---- the kernel -------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* x_tiles = smem;                                   // S_SMEM x 16 KB, each 1024-byte aligned
+    uint8_t* w_tiles = smem + S_SMEM * X_STAGE;                // S_SMEM x 8 KB
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + S_SMEM * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_stages = a.K / BK;
+    const int total_tiles = a.m_tiles * a.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S_SMEM; i++) { mbar_init(&bars->full_tma[i], 1); mbar_init(&bars->empty_smem[i], 1); }
+        for (int i = 0; i < S_A; i++) { mbar_init(&bars->full_a[i], DEQ_WARPS * 32); mbar_init(&bars->empty_a[i], 1); }
+        mbar_init(&bars->d_full, 1);
+        mbar_init(&bars->d_empty, EPI_WARPS * 32);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp == 0) {
+        // ---- TMA producer ----------------------------------------------------------------------------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int row0 = (tile % a.m_tiles) * BM, tok0 = (tile / a.m_tiles) * BN;
+                for (int ks = 0; ks < k_stages; ks++, it++) {
+                    const int s = it % S_SMEM;
+                    if (it >= S_SMEM && !mbar_wait(&bars->empty_smem[s], ((it / S_SMEM) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    mbar_expect_tx(&bars->full_tma[s], STAGE_BYTES);
+                    tma_load_2d(x_tiles + s * X_STAGE, &map_x, &bars->full_tma[s], ks * BK, tok0);
+                    tma_load_2d(w_tiles + s * W_STAGE, &map_w, &bars->full_tma[s], ks * (BK / 2), row0);
+                }
+            }
+            // Before leaving, see every copy this thread issued land (bounded), so that no bulk copy is in
+            // flight into the shared memory of a CTA that has exited.
+            const uint32_t first = it > S_SMEM ? it - S_SMEM : 0;
+            for (uint32_t j = first; j < it; j++) {
+                const int s = j % S_SMEM;
+                const uint64_t t0 = global_ns();
+                while (!mbar_try_wait(&bars->full_tma[s], (j / S_SMEM) & 1))
+                    if (global_ns() - t0 > WAIT_NS) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ------------------------------------------------------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, tile_i++) {
+                if (tile_i > 0 && !mbar_wait(&bars->d_empty, (tile_i - 1) & 1, &bars->abort_flag, a.err)) break;
+                tc_fence_after();
+                for (int ks = 0; ks < k_stages; ks++, it++) {
+                    const int s = it % S_SMEM, sa = it % S_A;
+                    if (!mbar_wait(&bars->full_tma[s], (it / S_SMEM) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    if (!mbar_wait(&bars->full_a[sa], (it / S_A) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t bdesc = smem_desc_sw128(smem_u32(x_tiles + s * X_STAGE));
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const uint32_t d_addr = tmem + D_COL0 + half * BN;
+                        const uint32_t a_addr = tmem + A_COL0 + (sa * 2 + half) * (BK / 2);
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; kk++)
+                            tc_mma_ts(d_addr, a_addr + kk * 8, bdesc + static_cast<uint64_t>(kk * 2), a.idesc, (ks | kk) != 0);
+                    }
+                    tc_commit(&bars->empty_smem[s]);   // X tile and packed W tile of stage s are free again
+                    tc_commit(&bars->empty_a[sa]);     // so is the A stage in tensor memory
+                }
+                if (ok) tc_commit(&bars->d_full);      // accumulators of this tile are complete
+            }
+        }
+    } else if (warp < EPI_WARP0) {
+        // ---- dequantisers: one thread per weight row ----------------------------------------------------------
+        const int half = (warp - DEQ_WARP0) >> 2;               // which 128-row MMA tile
+        const int quad = warp & 3;                              // TMEM lane quadrant this warp may touch
+        const int r = quad * 32 + lane;                         // row within the 128-row tile
+        const int gpr = a.K / a.gs;
+        const __half2 kMul = __halves2half2(__float2half(1.0f), __float2half(0.0625f));
+        const __half2 kSub = __halves2half2(__float2half(-1024.0f), __float2half(-64.0f));
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            const int row0 = (tile % a.m_tiles) * BM + half * 128;
+            const int row = min(row0 + r, a.O - 1);            // rows past the end read a valid row; never stored
+            const size_t srow = static_cast<size_t>(row) * gpr;
+            for (int ks = 0; ks < k_stages; ks++, it++) {
+                const int s = it % S_SMEM, sa = it % S_A;
+                // scale and bias of the (up to two) groups this 64-wide slice touches
+                const int g0 = (ks * BK) / a.gs, g1 = (ks * BK + 32) / a.gs;
+                const __half2 s0 = scale_pair(a.s, a.s_dtype, srow + g0), b0 = scale_pair(a.b, a.s_dtype, srow + g0);
+                __half2 s1 = s0, b1 = b0;
+                if (g1 != g0) { s1 = scale_pair(a.s, a.s_dtype, srow + g1); b1 = scale_pair(a.b, a.s_dtype, srow + g1); }
+                if (!mbar_wait(&bars->full_tma[s], (it / S_SMEM) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                const uint4* wp = reinterpret_cast<const uint4*>(w_tiles + s * W_STAGE + (half * 128 + r) * (BK / 2));
+                const uint4 p0 = wp[0], p1 = wp[1];
+                const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                uint32_t v[32];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const __half2 sc = i < 4 ? s0 : s1, bi = i < 4 ? b0 : b1;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        // byte j holds codes (2j, 2j+1): copy it into both halves, keep the low nibble in the low
+                        // half and the high nibble in the high half under the fp16 exponent of 1024, then
+                        // (1024 + q0, 1024 + 16 q1) * (1, 1/16) - (1024, 64) = (q0, q1) exactly.
+                        const uint32_t dup = __byte_perm(words[i], 0u, 0x4040 | (j << 8) | j);
+                        const uint32_t h = (dup & 0x00F0000Fu) | 0x64006400u;
+                        const __half2 q = __hfma2(*reinterpret_cast<const __half2*>(&h), kMul, kSub);
+                        const __half2 wv = __hfma2(q, sc, bi);
+                        v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
+                    }
+                }
+                if (it >= S_A && !mbar_wait(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                tc_fence_after();
+                tc_st32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 + (sa * 2 + half) * (BK / 2), v);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(&bars->full_a[sa]);
+            }
+        }
+    } else {
+        // ---- epilogue: TMEM -> registers -> (+ row bias) -> global --------------------------------------------
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        uint32_t tile_i = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_i++) {
+            const int row0 = (tile % a.m_tiles) * BM, tok0 = (tile / a.m_tiles) * BN;
+            if (!mbar_wait(&bars->d_full, tile_i & 1, &bars->abort_flag, a.err)) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int half = 0; half < 2; half++) {
+                const int row = row0 + half * 128 + r;
+                const float rb = (a.bias != nullptr && row < a.O) ? load_scalar(a.bias, a.bias_dtype, row) : 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; c++) {
+                    uint32_t v[32];
+                    tc_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + D_COL0 + half * BN + c * 32, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (half == 1 && c == BN / 32 - 1) {
+                        // last read of the accumulators: the MMA warp may start the next tile
+                        tc_fence_before();
+                        mbar_arrive(&bars->d_empty);
+                    }
+                    if (row < a.O) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int tok = tok0 + c * 32 + j;
+                            if (tok < a.T)
+                                store_scalar(a.y, a.y_dtype, static_cast<size_t>(tok) * a.y_stride + row, __uint_as_float(v[j]) + rb);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+
+// bf16 -> fp16, eight elements per thread.  Values beyond the fp16 range are clamped to +-65504.
+__global__ void bf16_to_f16_kernel(const uint16_t* __restrict__ x, long long x_stride, __half* __restrict__ out, long long T, int K) {
+    const long long chunks = static_cast<long long>(K) / 8;
+    const long long n = T * chunks;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long t = i / chunks, c = i - t * chunks;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + t * x_stride + c * 8));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float lo = fminf(fmaxf(__uint_as_float(w[j] << 16), -65504.0f), 65504.0f);
+            const float hi = fminf(fmaxf(__uint_as_float(w[j] & 0xFFFF0000u), -65504.0f), 65504.0f);
+            const __half2 h = __floats2half2_rn(lo, hi);
+            o[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(out + t * K + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer, uint64_t row_bytes,
+                 uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count(int device) {
+    static int cached[64] = {};
+    if (device < 0 || device >= 64) return 148;
+    if (!cached[device]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+        cached[device] = n;
+    }
+    return cached[device];
+}
+
+// One stream-ordered memory pool per device for the scratch copy of bf16 activations; freed blocks stay
+// in the pool (release threshold = unlimited) so steady-state calls do not reach the driver's allocator.
+cudaMemPool_t scratch_pool(int device) {
+    static cudaMemPool_t pools[64] = {};
+    static std::mutex mu;
+    if (device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!pools[device]) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = device;
+        cudaMemPool_t p = nullptr;
+        if (cudaMemPoolCreate(&p, &props) != cudaSuccess) return nullptr;
+        uint64_t keep = ~0ull;
+        cudaMemPoolSetAttribute(p, cudaMemPoolAttrReleaseThreshold, &keep);
+        pools[device] = p;
+    }
+    return pools[device];
+}
+
+}  // namespace
+
+int qgemm_tile_tokens(const GemmLayer& L, int x_dtype, long long x_stride, const void* x, long long T) {
+    if (L.bits != 4 || L.K % BK != 0 || L.gs % 32 != 0 || L.O < 1 || T < 1) return 0;
+    if (x_dtype != DT_F16 && x_dtype != DT_BF16) return 0;
+    if ((reinterpret_cast<uintptr_t>(L.w) & 15u) != 0) return 0;
+    if (x != nullptr && ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (x_stride * 2) % 16 != 0)) return 0;
+    if (T > 0x7FFFFFFFLL) return 0;
+    return BN;
+}
+
+cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why) {
+    *why = "";
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, [] {
+        attr_err = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess) { *why = "shared-memory opt-in"; return attr_err; }
+    // bf16 activations: fp16 copy in stream-ordered scratch (see the header comment).
+    const void* x = c.x;
+    long long x_stride = c.x_stride;
+    __half* scratch = nullptr;
+    if (c.x_dtype == DT_BF16) {
+        cudaMemPool_t pool = scratch_pool(L.device);
+        if (!pool) { *why = "scratch pool"; return cudaErrorMemoryAllocation; }
+        cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), static_cast<size_t>(c.T) * L.K * 2, pool, st);
+        if (e != cudaSuccess) { *why = "scratch allocation"; return e; }
+        const long long n = c.T * (L.K / 8);
+        const unsigned blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 8 ? n / 256 + 1 : 148LL * 8);
+        bf16_to_f16_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_stride, scratch, c.T, L.K);
+        x = scratch;
+        x_stride = L.K;
+    }
+    CUtensorMap map_w, map_x;
+    if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),
+                     static_cast<uint64_t>(L.K) / 2, BK / 2, BM, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+        if (scratch) cudaFreeAsync(scratch, st);
+        *why = "tensor map of the packed weights";
+        return cudaErrorInvalidValue;
+    }
+    if (!make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT16, x, static_cast<uint64_t>(L.K), static_cast<uint64_t>(c.T),
+                     static_cast<uint64_t>(x_stride) * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        if (scratch) cudaFreeAsync(scratch, st);
+        *why = "tensor map of the activations";
+        return cudaErrorInvalidValue;
+    }
+    GemmArgs a;
+    a.s = L.s; a.b = L.b; a.bias = L.bias; a.y = c.y; a.err = c.err; a.y_stride = c.y_stride;
+    a.s_dtype = L.s_dtype; a.bias_dtype = L.bias_dtype; a.y_dtype = c.y_dtype;
+    a.O = L.O; a.K = L.K; a.gs = L.gs; a.T = static_cast<int>(c.T);
+    a.m_tiles = (L.O + BM - 1) / BM;
+    a.n_tiles = static_cast<int>((c.T + BN - 1) / BN);
+    // instruction descriptor: fp32 accumulate (bit 4), A and B fp16 (format 0 at bits 7 and 10), both K-major,
+    // N >> 3 at bit 17, M >> 4 at bit 24
+    a.idesc = (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+    const long long tiles = static_cast<long long>(a.m_tiles) * a.n_tiles;
+    const int sms = sm_count(L.device);
+    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+    qgemm4_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
+    const cudaError_t launched = cudaGetLastError();
+    if (scratch) cudaFreeAsync(scratch, st);      // stream-ordered: released after the GEMM has read it
+    return launched;
+}
+
+}  // namespace mlxq
