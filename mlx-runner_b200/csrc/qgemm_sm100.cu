@@ -1,20 +1,26 @@
 // Prefill dequant-GEMM for sm_100a: Y[T, O] = X[T, K] . W[O, K]^T with W in the 4-bit MLX affine format.
 //
 // Mapping onto the 5th-generation tensor cores (tcgen05):
-//   * The weights are the A operand and live in TENSOR MEMORY, not shared memory.  One thread owns one
-//     weight row of the tile: it reads the row's 32 packed bytes of the current 64-wide K slice from shared
-//     memory (staged there by TMA), dequantises them to fp16 (w = scale*q + bias, the group's scale and
-//     bias in registers) and writes the 64 halves to its own TMEM lane with one tcgen05.st.  A in TMEM
-//     needs no swizzled shared-memory tile and costs no shared-memory bandwidth on the MMA side.
+//   * The weights are the A operand and live in TENSOR MEMORY, not shared memory.  A thread owns half a
+//     weight row of the tile's current 64-wide K slice: it reads the 16 packed bytes from shared memory
+//     (staged there by TMA), dequantises the 32 codes to fp16 (w = scale*q + bias, the group's scale and
+//     bias in registers) and writes them to its own TMEM lane with one tcgen05.st.  A in TMEM needs no
+//     swizzled shared-memory tile and costs no shared-memory bandwidth on the MMA side.
+//   * Dequantisation is three logic/shift ops and four half2 FMAs per eight codes: a masked nibble left at
+//     bits 4..7 of a half is the subnormal q * 2^-20, so w = fma(nibble, scale * 2^20, bias) needs no
+//     conversion.  (Scales of 2^-4 and above, where scale * 2^20 would leave fp16, take an exact two-step
+//     path.)  The mask pairs codes (i, i+4) of each eight, so the activations are staged with the matching
+//     order 0,4,1,5,2,6,3,7 inside every eight.
 //   * The activations are the B operand: TMA loads [128 tokens x 64] 16-bit tiles with the 128-byte swizzle
 //     and tcgen05.mma reads them through a shared-memory descriptor.  Both operands are fp16: a kind::f16
 //     MMA whose descriptor names fp16 for A and bf16 for B raises an illegal-instruction error on B200, and
-//     bf16 weights would cost 2^-9 per weight, so bf16 activations are first converted to fp16 (exact for
-//     |x| in [6.1e-5, 65504], clamped above) by a small kernel into stream-ordered scratch memory.
+//     bf16 weights would cost 2^-9 per weight, so a small kernel first writes the activations as fp16 (bf16
+//     input: exact for |x| in [6.1e-5, 65504], clamped above) in the staged order into stream-ordered
+//     scratch memory.
 //   * One CTA computes a 256 (rows) x 128 (tokens) output tile as two M=128 MMAs that share every B tile,
 //     accumulating in fp32 in TMEM (2 x 128 columns), K = 16 per instruction, issued by one thread.
-//   * Warp roles: warp 0 TMA producer, warp 1 MMA issuer (and TMEM allocator), warps 2-9 dequantisers
-//     (two warpgroups, one per 128-row half), warps 10-13 epilogue (tcgen05.ld -> row bias -> store).
+//   * Warp roles: warp 0 TMA producer, warp 1 MMA issuer (and TMEM allocator), warps 2-17 dequantisers
+//     (row half x K half x lane quadrant), warps 18-21 epilogue (tcgen05.ld -> row bias -> store).
 //   * Rings: 8 shared-memory stages (24 KB each: X tile + packed W tile) and 4 TMEM stages for A.
 //     All hand-offs are mbarriers; MMA completion is signalled with tcgen05.commit.
 //   * The kernel is persistent: min(#tiles, #SMs) CTAs walk the tile list; row tiles vary fastest so the
@@ -43,8 +49,8 @@ constexpr int S_A = 4;                  // TMEM stages of the A operand
 constexpr int X_STAGE = BN * BK * 2;    // 16384 bytes
 constexpr int W_STAGE = BM * BK / 2;    // 8192 bytes (4-bit codes)
 constexpr int STAGE_BYTES = X_STAGE + W_STAGE;
-constexpr int NUM_THREADS = 14 * 32;
-constexpr int DEQ_WARP0 = 2, DEQ_WARPS = 8, EPI_WARP0 = 10, EPI_WARPS = 4;
+constexpr int NUM_THREADS = 22 * 32;
+constexpr int DEQ_WARP0 = 2, DEQ_WARPS = 16, EPI_WARP0 = 18, EPI_WARPS = 4;
 constexpr int TMEM_COLS = 512;
 constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
 constexpr int A_COL0 = 2 * BN;          // A ring: S_A stages x 2 halves x 32 columns
@@ -172,13 +178,15 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             }
         }
     } else if (warp < EPI_WARP0) {
-        // ---- dequantisers: one thread per weight row ----------------------------------------------------------
-        const int half = (warp - DEQ_WARP0) >> 2;               // which 128-row MMA tile
+        // ---- dequantisers: one thread per (weight row, half of the 64-wide K slice) ---------------------------
+        const int dw = warp - DEQ_WARP0;
+        const int khalf = dw >> 3;                              // which 32 codes of the slice
+        const int half = (dw >> 2) & 1;                         // which 128-row MMA tile
         const int quad = warp & 3;                              // TMEM lane quadrant this warp may touch
         const int r = quad * 32 + lane;                         // row within the 128-row tile
         const int gpr = a.K / a.gs;
-        const __half2 kMul = __halves2half2(__float2half(1.0f), __float2half(0.0625f));
-        const __half2 kSub = __halves2half2(__float2half(-1024.0f), __float2half(-64.0f));
+        const __half2 kMul = __halves2half2(__float2half(0.0625f), __float2half(0.0625f));
+        const __half2 kSub = __halves2half2(__float2half(-64.0f), __float2half(-64.0f));
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
@@ -187,34 +195,38 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const size_t srow = static_cast<size_t>(row) * gpr;
             for (int ks = 0; ks < k_stages; ks++, it++) {
                 const int s = it % S_SMEM, sa = it % S_A;
-                // scale and bias of the (up to two) groups this 64-wide slice touches
-                const int g0 = (ks * BK) / a.gs, g1 = (ks * BK + 32) / a.gs;
-                const __half2 s0 = scale_pair(a.s, a.s_dtype, srow + g0), b0 = scale_pair(a.b, a.s_dtype, srow + g0);
-                __half2 s1 = s0, b1 = b0;
-                if (g1 != g0) { s1 = scale_pair(a.s, a.s_dtype, srow + g1); b1 = scale_pair(a.b, a.s_dtype, srow + g1); }
+                // scale and bias of the group these 32 codes belong to (groups are multiples of 32 codes)
+                const int grp = (ks * BK + khalf * 32) / a.gs;
+                const float sf = load_scalar(a.s, a.s_dtype, srow + grp);
+                const __half2 bi = scale_pair(a.b, a.s_dtype, srow + grp);
+                const bool small = fabsf(sf) < 0.0624f;         // scale * 2^20 stays inside fp16
+                const __half2 sc = __float2half2_rn(small ? sf * 1048576.0f : sf);
                 if (!mbar_wait(&bars->full_tma[s], (it / S_SMEM) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
-                const uint4* wp = reinterpret_cast<const uint4*>(w_tiles + s * W_STAGE + (half * 128 + r) * (BK / 2));
-                const uint4 p0 = wp[0], p1 = wp[1];
-                const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                uint32_t v[32];
+                const uint4 pk = *reinterpret_cast<const uint4*>(w_tiles + s * W_STAGE + (half * 128 + r) * (BK / 2) + khalf * 16);
+                const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+                uint32_t v[16];
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const __half2 sc = i < 4 ? s0 : s1, bi = i < 4 ? b0 : b1;
+                for (int i = 0; i < 4; i++) {
+                    // nibbles (0,4), (1,5), (2,6), (3,7) of the word, each pair brought to bits 4..7 of its half
+                    const uint32_t n[4] = {(words[i] << 4) & 0x00F000F0u, words[i] & 0x00F000F0u,
+                                           (words[i] >> 4) & 0x00F000F0u, (words[i] >> 8) & 0x00F000F0u};
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        // byte j holds codes (2j, 2j+1): copy it into both halves, keep the low nibble in the low
-                        // half and the high nibble in the high half under the fp16 exponent of 1024, then
-                        // (1024 + q0, 1024 + 16 q1) * (1, 1/16) - (1024, 64) = (q0, q1) exactly.
-                        const uint32_t dup = __byte_perm(words[i], 0u, 0x4040 | (j << 8) | j);
-                        const uint32_t h = (dup & 0x00F0000Fu) | 0x64006400u;
-                        const __half2 q = __hfma2(*reinterpret_cast<const __half2*>(&h), kMul, kSub);
-                        const __half2 wv = __hfma2(q, sc, bi);
+                        __half2 wv;
+                        if (small) {
+                            // the masked nibble is the subnormal q * 2^-20; scale carries the 2^20
+                            wv = __hfma2(*reinterpret_cast<const __half2*>(&n[j]), sc, bi);
+                        } else {
+                            // large scale: (1024 + 16 q) / 16 - 64 = q exactly, then q * scale + bias
+                            const uint32_t h = n[j] | 0x64006400u;
+                            wv = __hfma2(__hfma2(*reinterpret_cast<const __half2*>(&h), kMul, kSub), sc, bi);
+                        }
                         v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
                     }
                 }
                 if (it >= S_A && !mbar_wait(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                 tc_fence_after();
-                tc_st32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 + (sa * 2 + half) * (BK / 2), v);
+                tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 + (sa * 2 + half) * (BK / 2) + khalf * 16, v);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 mbar_arrive(&bars->full_a[sa]);
@@ -265,24 +277,29 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 }
 
 
-// bf16 -> fp16, eight elements per thread.  Values beyond the fp16 range are clamped to +-65504.
-__global__ void bf16_to_f16_kernel(const uint16_t* __restrict__ x, long long x_stride, __half* __restrict__ out, long long T, int K) {
+// Activations -> fp16 in the staged order (0,4,1,5,2,6,3,7 inside every eight), eight elements per thread.
+// bf16 values beyond the fp16 range are clamped to +-65504.
+__global__ void stage_x_kernel(const uint16_t* __restrict__ x, int is_bf16, long long x_stride, __half* __restrict__ out, long long T, int K) {
     const long long chunks = static_cast<long long>(K) / 8;
     const long long n = T * chunks;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long t = i / chunks, c = i - t * chunks;
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + t * x_stride + c * 8));
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        uint32_t o[4];
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        if (is_bf16) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float lo = fminf(fmaxf(__uint_as_float(w[j] << 16), -65504.0f), 65504.0f);
-            const float hi = fminf(fmaxf(__uint_as_float(w[j] & 0xFFFF0000u), -65504.0f), 65504.0f);
-            const __half2 h = __floats2half2_rn(lo, hi);
-            o[j] = *reinterpret_cast<const uint32_t*>(&h);
+            for (int j = 0; j < 4; j++) {
+                const float lo = fminf(fmaxf(__uint_as_float(w[j] << 16), -65504.0f), 65504.0f);
+                const float hi = fminf(fmaxf(__uint_as_float(w[j] & 0xFFFF0000u), -65504.0f), 65504.0f);
+                const __half2 h = __floats2half2_rn(lo, hi);
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
         }
-        *reinterpret_cast<uint4*>(out + t * K + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        // w = (x0,x1) (x2,x3) (x4,x5) (x6,x7)  ->  (x0,x4) (x1,x5) (x2,x6) (x3,x7)
+        const uint4 o = make_uint4(__byte_perm(w[0], w[2], 0x5410), __byte_perm(w[0], w[2], 0x7632),
+                                   __byte_perm(w[1], w[3], 0x5410), __byte_perm(w[1], w[3], 0x7632));
+        *reinterpret_cast<uint4*>(out + t * K + c * 8) = o;
     }
 }
 
@@ -369,18 +386,18 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
         attr_err = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     });
     if (attr_err != cudaSuccess) { *why = "shared-memory opt-in"; return attr_err; }
-    // bf16 activations: fp16 copy in stream-ordered scratch (see the header comment).
+    // The activations are rewritten as fp16 in the staged order into stream-ordered scratch (see the header).
     const void* x = c.x;
     long long x_stride = c.x_stride;
     __half* scratch = nullptr;
-    if (c.x_dtype == DT_BF16) {
+    {
         cudaMemPool_t pool = scratch_pool(L.device);
         if (!pool) { *why = "scratch pool"; return cudaErrorMemoryAllocation; }
         cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), static_cast<size_t>(c.T) * L.K * 2, pool, st);
         if (e != cudaSuccess) { *why = "scratch allocation"; return e; }
         const long long n = c.T * (L.K / 8);
         const unsigned blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 8 ? n / 256 + 1 : 148LL * 8);
-        bf16_to_f16_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_stride, scratch, c.T, L.K);
+        stage_x_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_dtype == DT_BF16 ? 1 : 0, c.x_stride, scratch, c.T, L.K);
         x = scratch;
         x_stride = L.K;
     }

@@ -52,41 +52,36 @@ size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, TmaPlan& tp) {
     if (p.passes > 4) return 0;
     int lb, kb;
     unit_for(bits, lb, kb);
+    (void)lb;
     const int K = q.K, groups = K / q.gs, sbytes = dtype_size(q.s_dtype);
-    const int steps = K / kb, step_bytes = 4 * lb;
-    // parts must hold multiples of 8 rows (the 8-row halves of a block are copied whole) and be aligned
+    // Eight consecutive rows are copied as one run: parts must hold multiples of 8 rows and be 16-byte aligned.
+    if (q.total_rows < 8) return 0;
     for (int i = 0; i < q.n_parts; i++) {
         if (q.part[i].rows % 8 != 0) return 0;
-        if ((reinterpret_cast<uintptr_t>(q.part[i].s) & 15u) || (reinterpret_cast<uintptr_t>(q.part[i].b) & 15u)) return 0;
+        if ((reinterpret_cast<uintptr_t>(q.part[i].w) & 15u) || (reinterpret_cast<uintptr_t>(q.part[i].s) & 15u) ||
+            (reinterpret_cast<uintptr_t>(q.part[i].b) & 15u))
+            return 0;
     }
-    const int unit = TMA_CONSUMERS << p.spg_shift;          // keep every consumer busy and groups whole
-    int kc = (36 * 1024 / 16 - 64) / step_bytes;
-    kc = kc / unit * unit;
-    if (kc < unit) kc = unit;
-    if (kc > steps) kc = align_up(steps, 1 << p.spg_shift);
-    tp.kc_steps = kc;
-    tp.n_chunks = (steps + kc - 1) / kc;
-    tp.chunk_bytes = kc * step_bytes;
-    const int rem = tp.chunk_bytes % 128;
-    tp.wstride = tp.chunk_bytes + (rem == 64 ? 0 : (64 - rem + 128) % 128);
-    tp.stage_bytes = align_up(16 * tp.wstride, 128);
-    tp.half_scale_bytes = 8 * groups * sbytes;
-    tp.scale_buf_bytes = align_up(4 * tp.half_scale_bytes, 128);
+    const long long w_bytes = 8LL * K * bits / 8;
+    if (w_bytes > 96 * 1024) return 0;
+    tp.w_bytes = static_cast<int>(w_bytes);
+    tp.s_bytes = 8 * groups * sbytes;
+    tp.stage_bytes = align_up(tp.w_bytes + 2 * tp.s_bytes, 128);
     tp.n_blocks = (q.total_rows + 15) / 16;
     int np = 1;
     while (np < p.passes) np *= 2;
     int off = align_up(p.xn * p.xstride * 2, 16);
     tp.off_xsum = off; off += align_up(p.xn * groups * 4, 16);
     tp.off_csum = off; off += align_up(tokens * (K / 8) * 4, 16);
-    tp.off_part = off; off += 2 * TMA_CONSUMERS * np * 128 * 4;
-    tp.off_scale = align_up(off, 128); off = tp.off_scale + 2 * tp.scale_buf_bytes;
+    tp.off_part = off; off += TMA_SLOTS * TMA_CONSUMERS * np * 128 * 4;
     tp.off_bars = align_up(off, 16); off = tp.off_bars + static_cast<int>(sizeof(TmaBars));
     tp.off_stage = align_up(off, 128);
     const int room = SMEM_BUDGET - tp.off_stage;
-    if (room < 2 * tp.stage_bytes) return 0;
-    tp.ns = room / tp.stage_bytes;
-    if (tp.ns > TMA_MAX_STAGES) tp.ns = TMA_MAX_STAGES;
-    return static_cast<size_t>(tp.off_stage) + static_cast<size_t>(tp.ns) * tp.stage_bytes;
+    int ns = room / tp.stage_bytes;
+    if (ns > TMA_MAX_STAGES) ns = TMA_MAX_STAGES;
+    if (ns < 2) return 0;
+    tp.ns = ns;
+    return static_cast<size_t>(tp.off_stage) + static_cast<size_t>(ns) * tp.stage_bytes;
 }
 
 cudaError_t launch_qmv_tma(int bits, const MmaParams& p, const TmaPlan& tp, size_t smem, int sms, cudaStream_t st) {
