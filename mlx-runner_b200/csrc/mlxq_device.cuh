@@ -24,6 +24,18 @@ __device__ __forceinline__ float load_scalar(const void* p, int dt, size_t i) {
     return __uint_as_float(static_cast<uint32_t>(u) << 16);
 }
 
+// Split form for software prefetching: the load returns raw bits (nothing depends on it, so the warp does not
+// wait), the conversion happens where the value is used.
+__device__ __forceinline__ uint32_t load_scalar_raw(const void* p, int dt, size_t i) {
+    if (dt == DT_F32) return __float_as_uint(__ldg(reinterpret_cast<const float*>(p) + i));
+    return __ldg(reinterpret_cast<const unsigned short*>(p) + i);
+}
+__device__ __forceinline__ float scalar_from_raw(uint32_t raw, int dt) {
+    if (dt == DT_F32) return __uint_as_float(raw);
+    if (dt == DT_F16) return __half2float(__ushort_as_half(static_cast<unsigned short>(raw)));
+    return __uint_as_float(raw << 16);
+}
+
 // The same for a shared-memory (or any generic) address: plain loads, no read-only cache hint.
 __device__ __forceinline__ float smem_scalar(const void* p, int dt, size_t i) {
     if (dt == DT_F32) return reinterpret_cast<const float*>(p)[i];

@@ -19,9 +19,14 @@
 //     scratch memory.
 //   * One CTA computes a 256 (rows) x 128 (tokens) output tile as two M=128 MMAs that share every B tile,
 //     accumulating in fp32 in TMEM (2 x 128 columns), K = 16 per instruction, issued by one thread.
-//   * Warp roles: warp 0 TMA producer, warp 1 MMA issuer (and TMEM allocator), warps 2-17 dequantisers
-//     (row half x K half x lane quadrant), warps 18-21 epilogue (tcgen05.ld -> row bias -> store).
-//   * Rings: 8 shared-memory stages (24 KB each: X tile + packed W tile) and 4 TMEM stages for A.
+//   * Warp roles: warp 0 TMA producer of activation tiles, warp 1 MMA issuer (and TMEM allocator), warp 2 TMA
+//     producer of weight slabs (its own warp, so weights run ahead of the activation ring), warps 4-19
+//     dequantisers (row half x K half x lane quadrant).  The same sixteen warps run the epilogue
+//     (tcgen05.ld -> row bias -> store, a quarter of the tile's columns per warp): a tile's epilogue is done
+//     after the first A stages of the NEXT tile are written, so the MMAs restart on a full ring.
+//   * Rings: 6 shared-memory stages of activations (16 KB), 3 slabs of packed weights (256 rows x 128 bytes =
+//     four K stages per TMA copy: a tile of 32-byte rows costs the TMA unit as many requests as one of
+//     128-byte rows and starved the MMAs) and 4 TMEM stages for A.
 //     All hand-offs are mbarriers; MMA completion is signalled with tcgen05.commit.
 //   * The kernel is persistent: min(#tiles, #SMs) CTAs walk the tile list; row tiles vary fastest so the
 //     CTAs running together share activation tiles in L2.
@@ -39,25 +44,37 @@
 
 namespace mlxq {
 
+#ifdef MLXQ_TRACE
+// Timeline probe for development builds.
+__device__ unsigned long long g_gemm_trace[148 * 256];
+#define GTRACE(slot) do { if ((slot) < 256) g_gemm_trace[blockIdx.x * 256 + (slot)] = global_ns(); } while (0)
+#else
+#define GTRACE(slot) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int BM = 256;                 // weight rows per CTA tile (two M=128 MMA tiles)
 constexpr int BN = 128;                 // tokens per tile
 constexpr int BK = 64;                  // K slice per stage
-constexpr int S_SMEM = 8;               // shared-memory stages
+constexpr int S_X = 6;                  // shared-memory stages of the activation tile
+constexpr int S_W = 3;                  // shared-memory slabs of packed weights (one slab = W_SPAN stages of K)
+constexpr int W_SPAN = 4;               // K stages per weight slab: 256 codes = 128 bytes per row and TMA request
 constexpr int S_A = 4;                  // TMEM stages of the A operand
 constexpr int X_STAGE = BN * BK * 2;    // 16384 bytes
-constexpr int W_STAGE = BM * BK / 2;    // 8192 bytes (4-bit codes)
-constexpr int STAGE_BYTES = X_STAGE + W_STAGE;
-constexpr int NUM_THREADS = 22 * 32;
-constexpr int DEQ_WARP0 = 2, DEQ_WARPS = 16, EPI_WARP0 = 18, EPI_WARPS = 4;
+constexpr int W_SLAB = BM * 128;        // 32768 bytes: 256 rows x 128 bytes, 128-byte swizzle
+constexpr int NUM_THREADS = 20 * 32;
+constexpr int W_PRODUCER = 2;           // warp that streams the packed weight slabs (warp 3 is idle)
+constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16;
 constexpr int TMEM_COLS = 512;
 constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
 constexpr int A_COL0 = 2 * BN;          // A ring: S_A stages x 2 halves x 32 columns
 
 struct Barriers {
-    uint64_t full_tma[S_SMEM];
-    uint64_t empty_smem[S_SMEM];
+    uint64_t full_x[S_X];
+    uint64_t empty_x[S_X];
+    uint64_t full_w[S_W];
+    uint64_t empty_w[S_W];
     uint64_t full_a[S_A];
     uint64_t empty_a[S_A];
     uint64_t d_full;
@@ -66,7 +83,7 @@ struct Barriers {
     int abort_flag;
 };
 
-constexpr int SMEM_BYTES = S_SMEM * STAGE_BYTES + sizeof(Barriers) + 1024;   // + alignment slack
+constexpr int SMEM_BYTES = S_X * X_STAGE + S_W * W_SLAB + sizeof(Barriers) + 1024;   // + alignment slack
 
 struct GemmArgs {
     const void* s;
@@ -77,6 +94,7 @@ struct GemmArgs {
     long long y_stride;
     int s_dtype, bias_dtype, y_dtype;
     int O, K, gs, T;
+    int gs_shift;        // log2(gs): group sizes are powers of two here
     int m_tiles, n_tiles;
     uint32_t idesc;
 };
@@ -96,19 +114,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* x_tiles = smem;                                   // S_SMEM x 16 KB, each 1024-byte aligned
-    uint8_t* w_tiles = smem + S_SMEM * X_STAGE;                // S_SMEM x 8 KB
-    Barriers* bars = reinterpret_cast<Barriers*>(smem + S_SMEM * STAGE_BYTES);
+    uint8_t* x_tiles = smem;                                   // S_X x 16 KB, each 1024-byte aligned
+    uint8_t* w_slabs = smem + S_X * X_STAGE;                   // S_W x 32 KB, each 1024-byte aligned
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + S_X * X_STAGE + S_W * W_SLAB);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_stages = a.K / BK;
     const int total_tiles = a.m_tiles * a.n_tiles;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < S_SMEM; i++) { mbar_init(&bars->full_tma[i], 1); mbar_init(&bars->empty_smem[i], 1); }
-        for (int i = 0; i < S_A; i++) { mbar_init(&bars->full_a[i], DEQ_WARPS * 32); mbar_init(&bars->empty_a[i], 1); }
+        for (int i = 0; i < S_X; i++) { mbar_init(&bars->full_x[i], 1); mbar_init(&bars->empty_x[i], 1); }
+        for (int i = 0; i < S_W; i++) { mbar_init(&bars->full_w[i], 1); mbar_init(&bars->empty_w[i], DEQ_WARPS); }
+        for (int i = 0; i < S_A; i++) { mbar_init(&bars->full_a[i], DEQ_WARPS); mbar_init(&bars->empty_a[i], 1); }
         mbar_init(&bars->d_full, 1);
-        mbar_init(&bars->d_empty, EPI_WARPS * 32);
+        mbar_init(&bars->d_empty, DEQ_WARPS);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -125,27 +144,46 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     if (warp == 0) {
         // ---- TMA producer ----------------------------------------------------------------------------------
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int row0 = (tile % a.m_tiles) * BM, tok0 = (tile / a.m_tiles) * BN;
+                const int tok0 = (tile / a.m_tiles) * BN, m_tile = tile % a.m_tiles;
                 for (int ks = 0; ks < k_stages; ks++, it++) {
-                    const int s = it % S_SMEM;
-                    if (it >= S_SMEM && !mbar_wait(&bars->empty_smem[s], ((it / S_SMEM) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
-                    mbar_expect_tx(&bars->full_tma[s], STAGE_BYTES);
-                    tma_load_2d(x_tiles + s * X_STAGE, &map_x, &bars->full_tma[s], ks * BK, tok0);
-                    tma_load_2d(w_tiles + s * W_STAGE, &map_w, &bars->full_tma[s], ks * (BK / 2), row0);
+                    const int s = it % S_X;
+                    if (it >= S_X && !mbar_wait(&bars->empty_x[s], ((it / S_X) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    mbar_expect_tx(&bars->full_x[s], X_STAGE);
+                    tma_load_2d(x_tiles + s * X_STAGE, &map_x, &bars->full_x[s], ks * BK, tok0);
+                    if (it < 24) GTRACE(160 + it);
                 }
             }
             // Before leaving, see every copy this thread issued land (bounded), so that no bulk copy is in
             // flight into the shared memory of a CTA that has exited.
-            const uint32_t first = it > S_SMEM ? it - S_SMEM : 0;
-            for (uint32_t j = first; j < it; j++) {
-                const int s = j % S_SMEM;
+            for (uint32_t j = it > S_X ? it - S_X : 0; j < it; j++) {
                 const uint64_t t0 = global_ns();
-                while (!mbar_try_wait(&bars->full_tma[s], (j / S_SMEM) & 1))
+                while (!mbar_try_wait(&bars->full_x[j % S_X], (j / S_X) & 1))
+                    if (global_ns() - t0 > WAIT_NS) break;
+            }
+        }
+    } else if (warp == W_PRODUCER) {
+        // ---- TMA producer of packed weights: one slab (256 rows x 128 bytes = W_SPAN stages of K) per copy ------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+            uint32_t wi = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int row0 = (tile % a.m_tiles) * BM;
+                for (int ks = 0; ks < k_stages; ks += W_SPAN, wi++) {
+                    const int sw = wi % S_W;
+                    if (wi >= S_W && !mbar_wait(&bars->empty_w[sw], ((wi / S_W) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    mbar_expect_tx(&bars->full_w[sw], W_SLAB);
+                    if (wi < 12) GTRACE(184 + wi);
+                    tma_load_2d(w_slabs + sw * W_SLAB, &map_w, &bars->full_w[sw], ks * (BK / 2), row0);
+                }
+            }
+            for (uint32_t j = wi > S_W ? wi - S_W : 0; j < wi; j++) {
+                const uint64_t t0 = global_ns();
+                while (!mbar_try_wait(&bars->full_w[j % S_W], (j / S_W) & 1))
                     if (global_ns() - t0 > WAIT_NS) break;
             }
         }
@@ -158,10 +196,11 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 if (tile_i > 0 && !mbar_wait(&bars->d_empty, (tile_i - 1) & 1, &bars->abort_flag, a.err)) break;
                 tc_fence_after();
                 for (int ks = 0; ks < k_stages; ks++, it++) {
-                    const int s = it % S_SMEM, sa = it % S_A;
-                    if (!mbar_wait(&bars->full_tma[s], (it / S_SMEM) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    const int s = it % S_X, sa = it % S_A;
+                    if (!mbar_wait(&bars->full_x[s], (it / S_X) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     if (!mbar_wait(&bars->full_a[sa], (it / S_A) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     tc_fence_after();
+                    if (tile_i == 0 && ks < 24) GTRACE(ks * 2);
                     const uint64_t bdesc = smem_desc_sw128(smem_u32(x_tiles + s * X_STAGE));
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
@@ -171,38 +210,135 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         for (int kk = 0; kk < BK / 16; kk++)
                             tc_mma_ts(d_addr, a_addr + kk * 8, bdesc + static_cast<uint64_t>(kk * 2), a.idesc, (ks | kk) != 0);
                     }
-                    tc_commit(&bars->empty_smem[s]);   // X tile and packed W tile of stage s are free again
+                    tc_commit(&bars->empty_x[s]);      // the activation tile of stage s is free again
                     tc_commit(&bars->empty_a[sa]);     // so is the A stage in tensor memory
+                    if (tile_i == 0 && ks < 24) GTRACE(ks * 2 + 1);
                 }
                 if (ok) tc_commit(&bars->d_full);      // accumulators of this tile are complete
             }
         }
-    } else if (warp < EPI_WARP0) {
+    } else if (warp >= DEQ_WARP0) {
         // ---- dequantisers: one thread per (weight row, half of the 64-wide K slice) ---------------------------
         const int dw = warp - DEQ_WARP0;
         const int khalf = dw >> 3;                              // which 32 codes of the slice
         const int half = (dw >> 2) & 1;                         // which 128-row MMA tile
         const int quad = warp & 3;                              // TMEM lane quadrant this warp may touch
         const int r = quad * 32 + lane;                         // row within the 128-row tile
-        const int gpr = a.K / a.gs;
+        const int gpr = a.K >> a.gs_shift;
         const __half2 kMul = __halves2half2(__float2half(0.0625f), __float2half(0.0625f));
         const __half2 kSub = __halves2half2(__float2half(-64.0f), __float2half(-64.0f));
-        uint32_t it = 0;
+        uint32_t it = 0, wi = 0, tile_i = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            const int row0 = (tile % a.m_tiles) * BM + half * 128;
+        // Epilogue of one tile: this warp drains its lane quadrant of one row half, 64 of the 128 token columns.
+        const int e_half = (dw >> 2) & 1, e_cols = (dw >> 3) * 64;
+        auto epilogue = [&](int tile, uint32_t index) {
+            const int row = (tile % a.m_tiles) * BM + e_half * 128 + r;
+            const int tok0 = (tile / a.m_tiles) * BN + e_cols;
+            if (!mbar_wait(&bars->d_full, index & 1, &bars->abort_flag, a.err)) return;
+            tc_fence_after();
+            const float rb = (a.bias != nullptr && row < a.O) ? load_scalar(a.bias, a.bias_dtype, row) : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < 2; c++) {
+                uint32_t v[32];
+                tc_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + D_COL0 + e_half * BN + e_cols + c * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (c == 1) {
+                    // last read of the accumulators by this warp: the MMA warp may start the next tile
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->d_empty);
+                }
+                if (row < a.O) {
+                    const int tok = tok0 + c * 32;
+                    const int nt = min(32, a.T - tok);
+                    if (a.y_dtype == DT_BF16) {
+                        __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(a.y) + static_cast<size_t>(tok) * a.y_stride + row;
+#pragma unroll
+                        for (int j = 0; j < 32; j++, yp += a.y_stride) if (j < nt) *yp = __float2bfloat16_rn(__uint_as_float(v[j]) + rb);
+                    } else if (a.y_dtype == DT_F16) {
+                        __half* yp = reinterpret_cast<__half*>(a.y) + static_cast<size_t>(tok) * a.y_stride + row;
+#pragma unroll
+                        for (int j = 0; j < 32; j++, yp += a.y_stride) if (j < nt) *yp = __float2half_rn(__uint_as_float(v[j]) + rb);
+                    } else {
+                        float* yp = reinterpret_cast<float*>(a.y) + static_cast<size_t>(tok) * a.y_stride + row;
+#pragma unroll
+                        for (int j = 0; j < 32; j++, yp += a.y_stride) if (j < nt) *yp = __uint_as_float(v[j]) + rb;
+                    }
+                }
+            }
+        };
+        int pending_tile = -1;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, tile_i++) {
+            const int m_tile = tile % a.m_tiles;
+            const int row0 = m_tile * BM + half * 128;
             const int row = min(row0 + r, a.O - 1);            // rows past the end read a valid row; never stored
             const size_t srow = static_cast<size_t>(row) * gpr;
+            // Scales and biases are fetched a whole weight slab (W_SPAN stages) ahead as raw bits -- a dependent
+            // global load (or a conversion of its result) per stage would put the load's full latency on every
+            // stage of every dequantising warp.  With 16-bit scales and one group per stage (group size 64) a
+            // slab's four scales are 8 contiguous bytes: one 64-bit load each for scales and biases.  The loads
+            // are volatile asm so that they are issued here and not re-materialised next to their use.
+            const bool packed4 = a.gs_shift == 6 && a.s_dtype != DT_F32 && (gpr & 3) == 0;
+            uint32_t s_nxt[W_SPAN], b_nxt[W_SPAN], s_cur[W_SPAN], b_cur[W_SPAN];
+            auto fetch_slab = [&](int ks0) {
+                if (packed4) {
+                    const unsigned short* sp = reinterpret_cast<const unsigned short*>(a.s) + srow + ks0;
+                    const unsigned short* bp = reinterpret_cast<const unsigned short*>(a.b) + srow + ks0;
+                    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(s_nxt[0]), "=r"(s_nxt[1]) : "l"(sp));
+                    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(b_nxt[0]), "=r"(b_nxt[1]) : "l"(bp));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < W_SPAN; j++) {
+                        const int grp = min(((ks0 + j) * BK + khalf * 32) >> a.gs_shift, gpr - 1);
+                        s_nxt[j] = load_scalar_raw(a.s, a.s_dtype, srow + grp);
+                        b_nxt[j] = load_scalar_raw(a.b, a.s_dtype, srow + grp);
+                    }
+                }
+            };
+            fetch_slab(0);
             for (int ks = 0; ks < k_stages; ks++, it++) {
-                const int s = it % S_SMEM, sa = it % S_A;
+                if (ks == S_A && pending_tile >= 0) {
+                    // The A ring now holds this tile's first stages; the MMAs wait for the previous tile's
+                    // accumulators to be read, which is what this does.
+                    epilogue(pending_tile, tile_i - 1);
+                    pending_tile = -1;
+                }
+                const int sa = it % S_A;
+                const int sub = ks % W_SPAN;                    // stage inside the weight slab
+                if (sub == 0) {
+                    wi++;                                       // same count as the producer: a new slab per W_SPAN stages of a tile
+#pragma unroll
+                    for (int j = 0; j < W_SPAN; j++) { s_cur[j] = s_nxt[j]; b_cur[j] = b_nxt[j]; }
+                    if (ks + W_SPAN < k_stages) fetch_slab(ks + W_SPAN);
+                }
+                const int sw = (wi - 1) % S_W;
                 // scale and bias of the group these 32 codes belong to (groups are multiples of 32 codes)
-                const int grp = (ks * BK + khalf * 32) / a.gs;
-                const float sf = load_scalar(a.s, a.s_dtype, srow + grp);
-                const __half2 bi = scale_pair(a.b, a.s_dtype, srow + grp);
+                uint32_t sraw, braw;
+                if (packed4) {
+                    const uint32_t sw2 = (sub & 2) ? s_cur[1] : s_cur[0], bw2 = (sub & 2) ? b_cur[1] : b_cur[0];
+                    sraw = (sub & 1) ? (sw2 >> 16) : (sw2 & 0xFFFFu);
+                    braw = (sub & 1) ? (bw2 >> 16) : (bw2 & 0xFFFFu);
+                } else {
+                    sraw = s_cur[0]; braw = b_cur[0];
+#pragma unroll
+                    for (int j = 1; j < W_SPAN; j++) if (sub == j) { sraw = s_cur[j]; braw = b_cur[j]; }
+                }
+                const float sf = scalar_from_raw(sraw, a.s_dtype);
+                const __half2 bi = __float2half2_rn(scalar_from_raw(braw, a.s_dtype));
                 const bool small = fabsf(sf) < 0.0624f;         // scale * 2^20 stays inside fp16
                 const __half2 sc = __float2half2_rn(small ? sf * 1048576.0f : sf);
-                if (!mbar_wait(&bars->full_tma[s], (it / S_SMEM) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
-                const uint4 pk = *reinterpret_cast<const uint4*>(w_tiles + s * W_STAGE + (half * 128 + r) * (BK / 2) + khalf * 16);
+                if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(208 + (wi - 1) * 2);
+                if (sub == 0 && !mbar_wait(&bars->full_w[sw], ((wi - 1) / S_W) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(209 + (wi - 1) * 2);
+                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4);
+                // row of 128 bytes, 16-byte chunk (sub*2 + khalf), stored with the 128-byte swizzle (chunk ^ row%8)
+                const int wr = half * 128 + r;
+                const uint4 pk = *reinterpret_cast<const uint4*>(w_slabs + sw * W_SLAB + wr * 128 + (((sub * 2 + khalf) ^ (wr & 7)) << 4));
+                if (sub == W_SPAN - 1 || ks == k_stages - 1) {
+                    // last read of the slab by this warp
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+                }
                 const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
                 uint32_t v[16];
 #pragma unroll
@@ -224,48 +360,21 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
                     }
                 }
+                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 1);
                 if (it >= S_A && !mbar_wait(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 2);
                 tc_fence_after();
                 tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 + (sa * 2 + half) * (BK / 2) + khalf * 16, v);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
-                mbar_arrive(&bars->full_a[sa]);
+                // one arrival per warp: hundreds of arrivals on one barrier word serialise in shared memory
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->full_a[sa]);
+                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 3);
             }
+            if (ok) pending_tile = tile;
         }
-    } else {
-        // ---- epilogue: TMEM -> registers -> (+ row bias) -> global --------------------------------------------
-        const int quad = warp & 3;
-        const int r = quad * 32 + lane;
-        uint32_t tile_i = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_i++) {
-            const int row0 = (tile % a.m_tiles) * BM, tok0 = (tile / a.m_tiles) * BN;
-            if (!mbar_wait(&bars->d_full, tile_i & 1, &bars->abort_flag, a.err)) break;
-            tc_fence_after();
-#pragma unroll 1
-            for (int half = 0; half < 2; half++) {
-                const int row = row0 + half * 128 + r;
-                const float rb = (a.bias != nullptr && row < a.O) ? load_scalar(a.bias, a.bias_dtype, row) : 0.0f;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; c++) {
-                    uint32_t v[32];
-                    tc_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + D_COL0 + half * BN + c * 32, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (half == 1 && c == BN / 32 - 1) {
-                        // last read of the accumulators: the MMA warp may start the next tile
-                        tc_fence_before();
-                        mbar_arrive(&bars->d_empty);
-                    }
-                    if (row < a.O) {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int tok = tok0 + c * 32 + j;
-                            if (tok < a.T)
-                                store_scalar(a.y, a.y_dtype, static_cast<size_t>(tok) * a.y_stride + row, __uint_as_float(v[j]) + rb);
-                        }
-                    }
-                }
-            }
-        }
+        if (pending_tile >= 0) epilogue(pending_tile, tile_i - 1);
     }
 
     tc_fence_before();
@@ -370,7 +479,7 @@ cudaMemPool_t scratch_pool(int device) {
 }  // namespace
 
 int qgemm_tile_tokens(const GemmLayer& L, int x_dtype, long long x_stride, const void* x, long long T) {
-    if (L.bits != 4 || L.K % BK != 0 || L.gs % 32 != 0 || L.O < 1 || T < 1) return 0;
+    if (L.bits != 4 || L.K % BK != 0 || L.K < 2 * S_A * BK || L.gs < 32 || (L.gs & (L.gs - 1)) != 0 || L.O < 1 || T < 1) return 0;
     if (x_dtype != DT_F16 && x_dtype != DT_BF16) return 0;
     if ((reinterpret_cast<uintptr_t>(L.w) & 15u) != 0) return 0;
     if (x != nullptr && ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (x_stride * 2) % 16 != 0)) return 0;
@@ -403,7 +512,7 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     }
     CUtensorMap map_w, map_x;
     if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),
-                     static_cast<uint64_t>(L.K) / 2, BK / 2, BM, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+                     static_cast<uint64_t>(L.K) / 2, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B)) {
         if (scratch) cudaFreeAsync(scratch, st);
         *why = "tensor map of the packed weights";
         return cudaErrorInvalidValue;
@@ -418,6 +527,8 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     a.s = L.s; a.b = L.b; a.bias = L.bias; a.y = c.y; a.err = c.err; a.y_stride = c.y_stride;
     a.s_dtype = L.s_dtype; a.bias_dtype = L.bias_dtype; a.y_dtype = c.y_dtype;
     a.O = L.O; a.K = L.K; a.gs = L.gs; a.T = static_cast<int>(c.T);
+    a.gs_shift = 0;
+    while ((1 << a.gs_shift) < L.gs) a.gs_shift++;
     a.m_tiles = (L.O + BM - 1) / BM;
     a.n_tiles = static_cast<int>((c.T + BN - 1) / BN);
     // instruction descriptor: fp32 accumulate (bit 4), A and B fp16 (format 0 at bits 7 and 10), both K-major,
