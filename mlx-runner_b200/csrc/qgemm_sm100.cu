@@ -234,12 +234,13 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         auto epilogue = [&](int tile, uint32_t index) {
             const int row = (tile % a.m_tiles) * BM + e_half * 128 + r;
             const int tok0 = (tile / a.m_tiles) * BN + e_cols;
-            if (!mbar_wait(&bars->d_full, index & 1, &bars->abort_flag, a.err)) return;
+            if (!mbar_wait_warp(&bars->d_full, index & 1, &bars->abort_flag, a.err)) return;
             tc_fence_after();
             const float rb = (a.bias != nullptr && row < a.O) ? load_scalar(a.bias, a.bias_dtype, row) : 0.0f;
 #pragma unroll 1
             for (int c = 0; c < 2; c++) {
                 uint32_t v[32];
+                __syncwarp();                                   // rows past O skip the stores below
                 tc_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + D_COL0 + e_half * BN + e_cols + c * 32, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (c == 1) {
@@ -328,7 +329,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 const bool small = fabsf(sf) < 0.0624f;         // scale * 2^20 stays inside fp16
                 const __half2 sc = __float2half2_rn(small ? sf * 1048576.0f : sf);
                 if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(208 + (wi - 1) * 2);
-                if (sub == 0 && !mbar_wait(&bars->full_w[sw], ((wi - 1) / S_W) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                if (sub == 0 && !mbar_wait_warp(&bars->full_w[sw], ((wi - 1) / S_W) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                 if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(209 + (wi - 1) * 2);
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4);
                 // row of 128 bytes, 16-byte chunk (sub*2 + khalf), stored with the 128-byte swizzle (chunk ^ row%8)
@@ -361,8 +362,9 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     }
                 }
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 1);
-                if (it >= S_A && !mbar_wait(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                if (it >= S_A && !mbar_wait_warp(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 2);
+                __syncwarp();                                   // the per-lane dequant branches end here
                 tc_fence_after();
                 tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 + (sa * 2 + half) * (BK / 2) + khalf * 16, v);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -380,6 +382,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
+        __syncwarp();                                           // lane 0 issued the MMAs alone
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }

@@ -121,7 +121,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         for (int blk = blockIdx.x; blk < tp.n_blocks; blk += gridDim.x, bi++) {
             const int slot = bi % TMA_SLOTS;
             float* blockpart = part + static_cast<size_t>(slot) * (TMA_CONSUMERS * NP * 128);
-            mbar_wait(&bars->part_full[slot], (bi / TMA_SLOTS) & 1, &bars->abort_flag, p.err);
+            mbar_wait_warp(&bars->part_full[slot], (bi / TMA_SLOTS) & 1, &bars->abort_flag, p.err);
             // stage 1: entry-wise sum over the consumer warps, four entries per lane per pass
             float4 acc[NP];
 #pragma unroll
@@ -268,8 +268,8 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
 #pragma unroll
                 for (int k = 0; k < NCH; k++) c[ps][k][i] = 0.0f;
             }
-        mbar_wait(&bars->full[st0], (it / tp.ns) & 1, &bars->abort_flag, p.err);
-        mbar_wait(&bars->full[st1], ((it + 1) / tp.ns) & 1, &bars->abort_flag, p.err);
+        mbar_wait_warp(&bars->full[st0], (it / tp.ns) & 1, &bars->abort_flag, p.err);
+        mbar_wait_warp(&bars->full[st1], ((it + 1) / tp.ns) & 1, &bars->abort_flag, p.err);
 
         const uint8_t* f0 = half0 + frag_off + s_begin * (4 * LB);
         const uint8_t* f1 = half1 + frag_off + s_begin * (4 * LB);
@@ -365,7 +365,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
 
         // deliver the partial sums to the reducer
         const int slot = bi % TMA_SLOTS;
-        if (bi >= TMA_SLOTS) mbar_wait(&bars->part_empty[slot], ((bi / TMA_SLOTS) - 1) & 1, &bars->abort_flag, p.err);
+        if (bi >= TMA_SLOTS) mbar_wait_warp(&bars->part_empty[slot], ((bi / TMA_SLOTS) - 1) & 1, &bars->abort_flag, p.err);
         float* mine = part + (static_cast<size_t>(slot) * TMA_CONSUMERS + warp) * (NP * 128);
 #pragma unroll
         for (int ps = 0; ps < NP; ps++)

@@ -58,6 +58,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* a
     return mbar_wait_slow(bar, parity, abort_flag, err);
 }
 
+// Whole-warp wait.  Every lane polls (each one needs the acquire for what it reads next) and the vote
+// brings the warp back together with one verdict: lanes leave a polling loop on different iterations, and a
+// ".sync.aligned" instruction (tcgen05.ld / tcgen05.st / mma.sync) issued before they have reconverged is
+// undefined -- in practice some lanes' TMEM stores were lost.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* abort_flag, unsigned* err) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, err));
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
