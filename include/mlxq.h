@@ -115,6 +115,24 @@ MLXQ_API int64_t mlxq_linear_row_offset(mlxq_linear_t h);
 MLXQ_API int mlxq_linear_forward(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, int64_t x_stride,
                                  void* y, int y_dtype, int64_t y_stride, int64_t T);
 
+/* mlxq_linear_forward for callers that cannot allocate device memory.  It has no counterpart in the reference.
+ * The tensor-core GEMM of mlxq_linear_forward stages an fp16 copy of the activations (T * in_dim * 2 bytes)
+ * in pool memory it allocates on the stream.  A host that has given all free device memory to its own caches,
+ * or that must not enter the CUDA allocator while it runs (an allocator lock held by the host, a latency
+ * budget that cannot absorb the allocator's device synchronisation), calls this entry point instead: the
+ * staged copy lives in a fixed 32 MiB array inside the library (MLXQ_STATIC_SCRATCH_BYTES), no cudaMalloc,
+ * cudaFree or other allocating routine is called, and results are the same as mlxq_linear_forward's.
+ *   - Batches with T * in_dim * 2 above the array's size are rejected with MLXQ_INVALID_ARGUMENT (split them).
+ *   - Batches the GEMM does not take (T <= 16, fp32 activations, other bit widths) run on kernels that use no
+ *     scratch memory, exactly as in mlxq_linear_forward.
+ *   - Every call on a device shares the one array, which keeps whatever the last call wrote: calls that
+ *     overlap on the GPU (different streams) race; order them on one stream or with events.
+ *   - The first call on each device looks up the array's device address and sets the kernel's shared-memory
+ *     attribute; make that first call before any stream capture begins. */
+#define MLXQ_STATIC_SCRATCH_BYTES (32u << 20)
+MLXQ_API int mlxq_linear_forward_static(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype,
+                                        int64_t x_stride, void* y, int y_dtype, int64_t y_stride, int64_t T);
+
 /* Linear.encodeFusedDecode, Transformer.swift:206-244: one launch computing the rows [A | B | C] of up
  * to three layers that satisfy mlxq_fusable(). */
 MLXQ_API int mlxq_fused_forward(const mlxq_linear_t* parts, int n_parts, mlxq_stream_t stream, const void* x,

@@ -19,6 +19,7 @@ F32, F16, BF16 = 0, 1, 2
 # gate activations (mlxq_act)
 ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 COMM_ID_BYTES = 128
+STATIC_SCRATCH_BYTES = 32 << 20     # MLXQ_STATIC_SCRATCH_BYTES
 
 
 class LinearDesc(C.Structure):
@@ -49,6 +50,8 @@ SIGNATURES = {
     "mlxq_linear_row_offset": (C.c_int64, [C.c_void_p]),
     "mlxq_linear_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int,
                                       C.c_int64, C.c_int64]),
+    "mlxq_linear_forward_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p,
+                                             C.c_int, C.c_int64, C.c_int64]),
     "mlxq_fused_forward": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
                                      C.c_void_p, C.c_int, C.c_int64, C.c_int64]),
     "mlxq_linear_forward_gated": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,

@@ -381,6 +381,33 @@ int mlxq_linear_forward(mlxq_linear_t h, mlxq_stream_t stream, const void* x, in
     return forward_impl(h, static_cast<cudaStream_t>(stream), x, x_dtype, x_stride, y, y_dtype, y_stride, T);
 }
 
+int mlxq_linear_forward_static(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, int64_t x_stride, void* y,
+                               int y_dtype, int64_t y_stride, int64_t T) {
+    if (!h) return fail(MLXQ_INVALID_ARGUMENT, "null layer");
+    if (T < 1) return fail(MLXQ_INVALID_ARGUMENT, "T = %lld", (long long)T);
+    if (int rc = check_x(x, x_dtype, x_stride, h->in_dim, T)) return rc;
+    if (!y || !valid_dtype(y_dtype)) return fail(MLXQ_INVALID_ARGUMENT, "y is null or has dtype %d", y_dtype);
+    if (T > 1 && y_stride < h->out_dim) return fail(MLXQ_INVALID_ARGUMENT, "y stride %lld < out_dim", (long long)y_stride);
+    DeviceGuard guard(h->device);
+    if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (gemm_tile_for(h, x_dtype, x_stride, x, T) > 0) {
+        const unsigned long long need = static_cast<unsigned long long>(T) * static_cast<unsigned long long>(h->in_dim) * 2ull;
+        if (need > qgemm_static_capacity())
+            return fail(MLXQ_INVALID_ARGUMENT, "%s: T * in_dim * 2 = %llu bytes of staged activations exceed the %zu-byte static scratch; "
+                        "split the batch or use mlxq_linear_forward", h->name.c_str(), need, qgemm_static_capacity());
+        GemmCall c;
+        c.x = x; c.x_dtype = x_dtype; c.x_stride = x_stride; c.y = y; c.y_dtype = y_dtype; c.y_stride = y_stride; c.T = T;
+        c.err = device_error_word(h->device);
+        const char* why = "";
+        cudaError_t err = launch_qgemm_static(gemm_layer(h), c, st, &why);
+        if (err != cudaSuccess) return fail(MLXQ_GPU_FAILURE, "qgemm launch: %s (%s)", cudaGetErrorString(err), why);
+        return MLXQ_OK;
+    }
+    // batches the GEMM does not take run on kernels that use no scratch memory at all
+    return run_qmv(&h, 1, st, x, x_dtype, x_stride, y, y_dtype, y_stride, T, nullptr, 0);
+}
+
 int mlxq_fusable(const mlxq_linear_t* parts, int n) {
     if (!parts || n < 1 || n > 3 || !parts[0]) return 0;
     const mlxq_linear* f = parts[0];

@@ -34,4 +34,9 @@ int qgemm_tile_tokens(const GemmLayer& L, int x_dtype, long long x_stride, const
 // Enqueues the GEMM.  Returns cudaSuccess, or an error with `why` filled in.
 cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why);
 
+// The same GEMM with its scratch in a fixed device array instead of pool memory: allocates nothing.
+// Returns cudaErrorInvalidValue (why = "batch exceeds the static scratch") beyond qgemm_static_capacity().
+size_t qgemm_static_capacity();
+cudaError_t launch_qgemm_static(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why);
+
 }  // namespace mlxq

@@ -546,4 +546,76 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     return launched;
 }
 
+// ---- the GEMM without any allocation -------------------------------------------------------------------------
+// Some hosts must not allocate device memory while they run: a serving loop that has handed every free byte
+// to its KV cache, a host whose allocator is locked during its hot loop, a caller inside a region where
+// cudaMalloc would synchronise the device.  For them the staged fp16 copy of the activations goes into this
+// fixed array instead of pool memory.  The array is part of the library image: every GPU that loads the
+// library holds its 32 MiB until the process exits.  Its contents are whatever the last call left; nothing in
+// it needs to start at zero (each call rewrites the [T, K] region it later reads).  All calls on a device share
+// it, so two calls that overlap on the GPU (different streams) race.
+constexpr size_t STATIC_SCRATCH_BYTES = 32u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+size_t qgemm_static_capacity() { return STATIC_SCRATCH_BYTES; }
+
+cudaError_t launch_qgemm_static(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why) {
+    *why = "";
+    if (static_cast<unsigned long long>(c.T) * static_cast<unsigned long long>(L.K) * 2ull > STATIC_SCRATCH_BYTES) {
+        *why = "batch exceeds the static scratch";
+        return cudaErrorInvalidValue;
+    }
+    // In host code the array's name is only a handle: the device address comes from cudaGetSymbolAddress, asked
+    // once per device with that device current (the caller has selected L.device).  This first call per device
+    // also opts the kernel into its shared-memory size; make it before any stream capture.
+    static std::mutex mu;
+    static __half* base[64] = {};
+    static bool attr_done[64] = {};
+    if (L.device < 0 || L.device >= 64) { *why = "device ordinal"; return cudaErrorInvalidDevice; }
+    __half* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!base[L.device]) {
+            void* p = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+            if (e != cudaSuccess) { *why = "address of the static scratch"; return e; }
+            base[L.device] = static_cast<__half*>(p);
+        }
+        if (!attr_done[L.device]) {
+            const cudaError_t e = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) { *why = "shared-memory opt-in"; return e; }
+            attr_done[L.device] = true;
+        }
+        scratch = base[L.device];
+    }
+    const long long n = c.T * (L.K / 8);
+    const unsigned blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 8 ? n / 256 + 1 : 148LL * 8);
+    stage_x_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_dtype == DT_BF16 ? 1 : 0, c.x_stride, scratch, c.T, L.K);
+    CUtensorMap map_w, map_x;
+    if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),
+                     static_cast<uint64_t>(L.K) / 2, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        *why = "tensor map of the packed weights";
+        return cudaErrorInvalidValue;
+    }
+    if (!make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT16, scratch, static_cast<uint64_t>(L.K), static_cast<uint64_t>(c.T),
+                     static_cast<uint64_t>(L.K) * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        *why = "tensor map of the activations";
+        return cudaErrorInvalidValue;
+    }
+    GemmArgs a;
+    a.s = L.s; a.b = L.b; a.bias = L.bias; a.y = c.y; a.err = c.err; a.y_stride = c.y_stride;
+    a.s_dtype = L.s_dtype; a.bias_dtype = L.bias_dtype; a.y_dtype = c.y_dtype;
+    a.O = L.O; a.K = L.K; a.gs = L.gs; a.T = static_cast<int>(c.T);
+    a.gs_shift = 0;
+    while ((1 << a.gs_shift) < L.gs) a.gs_shift++;
+    a.m_tiles = (L.O + BM - 1) / BM;
+    a.n_tiles = static_cast<int>((c.T + BN - 1) / BN);
+    a.idesc = (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+    const long long tiles = static_cast<long long>(a.m_tiles) * a.n_tiles;
+    const int sms = sm_count(L.device);
+    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+    qgemm4_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
+    return cudaGetLastError();
+}
+
 }  // namespace mlxq

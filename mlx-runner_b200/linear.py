@@ -237,6 +237,15 @@ class Linear:
         check(L.load().mlxq_linear_forward(self._h, _stream_handle(stream), _ptr(x), _act_dtype(x, xDtype), xStride,
                                            _ptr(y), _act_dtype(y, yDtype), yStride, T))
 
+    def encodeStatic(self, stream, x, xStride: int, y, yStride: int, T: int, xDtype: Optional[int] = None,
+                     yDtype: Optional[int] = None) -> None:
+        """``encode`` for hosts that must not allocate device memory while they run: the GEMM's staged copy
+        of the activations goes into the library's fixed 32 MiB array instead of pool memory.  Same results;
+        batches with ``T * inDim * 2`` bytes above the array are refused (``InvalidArgument``); calls that
+        overlap on the GPU share the array and race.  No counterpart in the reference."""
+        check(L.load().mlxq_linear_forward_static(self._h, _stream_handle(stream), _ptr(x), _act_dtype(x, xDtype),
+                                                  xStride, _ptr(y), _act_dtype(y, yDtype), yStride, T))
+
     @staticmethod
     def encodeFusedDecode(stream, parts: Sequence["Linear"], x, y, xStride: int = 0, yStride: int = 0, T: int = 1,
                           xDtype: Optional[int] = None, yDtype: Optional[int] = None) -> None:
