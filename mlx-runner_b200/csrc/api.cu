@@ -239,8 +239,8 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         // Preferred: the persistent kernel fed by TMA bulk copies (MLXQ_DECODE=mma keeps the register-fed one).
         const char* mode = getenv("MLXQ_DECODE");
         TmaPlan tp;
-        const size_t tsmem = (mode && strcmp(mode, "mma") == 0) || !mp.err ? 0 : qmv_tma_plan(parts[0]->bits, mp, static_cast<int>(T), tp);
-        cudaError_t err = tsmem ? launch_qmv_tma(parts[0]->bits, mp, tp, tsmem, device_sm_count(parts[0]->device), st)
+        const size_t tsmem = (mode && strcmp(mode, "mma") == 0) || !mp.err ? 0 : qmv_tma_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), tp);
+        cudaError_t err = tsmem ? launch_qmv_tma(parts[0]->bits, mp, tp, tsmem, st)
                                 : launch_qmv_mma(parts[0]->bits, mp, smem, st);
         if (err != cudaSuccess) return cuda_fail(err, "qmv (tensor-core) launch");
         return MLXQ_OK;

@@ -22,12 +22,23 @@
 
 namespace mlxq {
 
-constexpr int TMA_CONSUMERS = 16;                      // consumer warps (K splits of a block)
-constexpr int TMA_PRODUCER = TMA_CONSUMERS;            // warp index of the producer
-constexpr int TMA_REDUCER = TMA_CONSUMERS + 1;         // warp index of the reducer
-constexpr int TMA_THREADS = (TMA_CONSUMERS + 2) * 32;
+// A CTA has NC consumer warps (8: two CTAs per SM, each with half the shared memory; 16: one CTA per SM,
+// for calls whose staged activations need the room), then the producer warp, then the reducer warp.
+constexpr int TMA_MAX_CONSUMERS = 16;
 constexpr int TMA_MAX_STAGES = 12;                     // ring stages (one stage = 8 rows)
-constexpr int TMA_SLOTS = 4;                           // row blocks whose partial sums may be pending
+constexpr int TMA_SLOTS = 8;                           // most row blocks whose partial sums may be pending
+
+#ifdef MLXQ_TRACE
+// development aid: per-CTA timestamps of the pipeline's hand-offs (64 slots per CTA)
+__device__ unsigned long long g_tma_trace[148 * 64];
+#define TTRACE(slot) do { if (blockIdx.x < 148) g_tma_trace[blockIdx.x * 64 + (slot)] = global_ns(); } while (0)
+#else
+#define TTRACE(slot) do { } while (0)
+#endif
+
+#ifndef MLXQ_ABLATE
+#define MLXQ_ABLATE 0      // development aid: bit mask of kernel parts to leave out when timing (results are then wrong)
+#endif
 
 struct TmaPlan {
     int ns;              // ring stages (half blocks)
@@ -35,7 +46,13 @@ struct TmaPlan {
     int s_bytes;         // 8 rows of scales (or of biases)
     int stage_bytes;     // w_bytes + 2 * s_bytes, rounded up to 128
     int off_xsum, off_csum, off_part, off_stage, off_bars;   // shared-memory offsets
+    int off_zero;        // 256 bytes of zeros: the B fragment of lanes whose accumulator column is idle in a step
     int n_blocks;        // 16-row blocks
+    int ksplit;          // consumer warps that share one block along K (16, 8 or 4); 16 / ksplit blocks are in work at once
+    int slots;           // partial-sum slots in use (<= TMA_SLOTS)
+    int consumers;       // consumer warps per CTA (8 or 16)
+    int grid;            // CTAs to launch
+    int rowsum;          // 1: one token in one column set -- consumers hand over 16 row sums instead of 16 x 8 entries
 };
 
 struct TmaBars {
@@ -46,9 +63,10 @@ struct TmaBars {
     int abort_flag;
 };
 
-template <int BITS, int NP>
-__global__ void __launch_bounds__(TMA_THREADS, 1)
+template <int BITS, int NP, int NC>
+__global__ void __launch_bounds__((NC + 2) * 32, NC == 8 ? 2 : 1)
 qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
+    constexpr int TMA_CONSUMERS = NC, TMA_PRODUCER = NC, TMA_REDUCER = NC + 1;
     using U = MmaUnit<BITS>;
     constexpr int LB = U::LB, CL = U::CL, KB = U::KB, NW = U::NW, NM = U::NM;
     extern __shared__ __align__(128) uint8_t smem_tma[];
@@ -67,45 +85,67 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
     const int steps_total = K / KB;
     const size_t row_bytes = static_cast<size_t>(K) * BITS / 8;
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < tp.ns; i++) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], TMA_CONSUMERS); }
-        for (int i = 0; i < TMA_SLOTS; i++) { mbar_init(&bars->part_full[i], TMA_CONSUMERS); mbar_init(&bars->part_empty[i], 1); }
-        bars->abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // barriers are set up by one thread each
+    if (threadIdx.x == 0) { TTRACE(0); bars->abort_flag = 0; }
+    if (threadIdx.x < tp.ns) { mbar_init(&bars->full[threadIdx.x], 1); mbar_init(&bars->empty[threadIdx.x], tp.ksplit); }
+    if (threadIdx.x >= 32 && threadIdx.x < 32 + TMA_SLOTS) {
+        mbar_init(&bars->part_full[threadIdx.x - 32], tp.ksplit);
+        mbar_init(&bars->part_empty[threadIdx.x - 32], 1);
     }
+    if (threadIdx.x < 32 + TMA_SLOTS) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (threadIdx.x >= 64 && threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem_tma + tp.off_zero)[threadIdx.x - 64] = 0u;
     __syncthreads();
+    // Programmatic dependent launch: the next kernel of the stream (if it was launched to allow it) may be
+    // scheduled as soon as every CTA of this grid is resident, so its prologue and its weight copies overlap
+    // this grid's tail.  The other half of the contract is the griddepcontrol.wait below: nothing reads the
+    // activations, the row bias or the gate vector, and nothing writes y, before the previous grid is complete.
+    // The packed weights, scales and biases are read earlier: they are the layer's constants.
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // geometry of the column plan shared by consumers and reducer (see qmv_mma.cuh)
     const int gsh = p.gstep_shift, G = 1 << gsh, CY = p.cycle, spg_shift = p.spg_shift;
     const int cols_per_cycle = p.xn << gsh;
 
     if (warp == TMA_PRODUCER) {
-        // ---- producer: three bulk copies per half block (weights, scales, biases of 8 consecutive rows) -----
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int blk = blockIdx.x; blk < tp.n_blocks; blk += gridDim.x) {
-                for (int h = 0; h < 2; h++, it++) {
-                    const int st = it % tp.ns;
-                    if (it >= static_cast<uint32_t>(tp.ns))
-                        mbar_wait(&bars->empty[st], ((it / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
-                    // the half's first row, resolved to its layer part (a missing second half re-reads the first)
-                    int r = min(blk * 16 + 8 * h, q.total_rows - 8), pi = 0;
-                    if (q.n_parts > 1 && r >= q.part[0].rows) {
-                        r -= q.part[0].rows; pi = 1;
-                        if (q.n_parts > 2 && r >= q.part[1].rows) { r -= q.part[1].rows; pi = 2; }
-                    }
-                    uint8_t* dst = stages + static_cast<size_t>(st) * tp.stage_bytes;
-                    const size_t soff = static_cast<size_t>(r) * groups * sbytes;
+        // ---- producer: six lanes, one bulk copy each per block (weights, scales, biases of each 8-row half) ----
+        // A bulk copy costs its issuing thread ~70 ns, so the block's six copies leave from six lanes at once.
+        // The lane that copies a half's weights also posts the half's byte count on its barrier; a copy that
+        // lands before that only drives the count negative for a moment, the phase cannot complete without
+        // the arrival.
+        uint32_t n_it = 0;
+        if (lane < 6) {
+            const int h = lane / 3, j = lane - 3 * h;
+            if (lane == 0) TTRACE(1);
+            uint32_t it = h;
+            for (int blk = blockIdx.x; blk < tp.n_blocks; blk += gridDim.x, it += 2) {
+                const int st = it % tp.ns;
+                if (it >= static_cast<uint32_t>(tp.ns))
+                    mbar_wait(&bars->empty[st], ((it / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
+                // the half's first row, resolved to its layer part (a missing second half re-reads the first)
+                int r = min(blk * 16 + 8 * h, q.total_rows - 8), pi = 0;
+                if (q.n_parts > 1 && r >= q.part[0].rows) {
+                    r -= q.part[0].rows; pi = 1;
+                    if (q.n_parts > 2 && r >= q.part[1].rows) { r -= q.part[1].rows; pi = 2; }
+                }
+                uint8_t* dst = stages + static_cast<size_t>(st) * tp.stage_bytes;
+                const size_t soff = static_cast<size_t>(r) * groups * sbytes;
+                if (j == 0) {
                     mbar_expect_tx(&bars->full[st], tp.w_bytes + 2 * tp.s_bytes);
                     bulk_load(dst, q.part[pi].w + static_cast<size_t>(r) * row_bytes, tp.w_bytes, &bars->full[st]);
+                } else if (j == 1) {
                     bulk_load(dst + tp.w_bytes, static_cast<const char*>(q.part[pi].s) + soff, tp.s_bytes, &bars->full[st]);
+                } else {
                     bulk_load(dst + tp.w_bytes + tp.s_bytes, static_cast<const char*>(q.part[pi].b) + soff, tp.s_bytes, &bars->full[st]);
                 }
+                if (j == 0 && it < 12) TTRACE(2 + it);
             }
+            n_it = it - h;
+        }
+        __syncwarp();
+        if (lane == 0) {
             // see every copy of the last ring turn land before leaving (bounded)
-            const uint32_t first = it > static_cast<uint32_t>(tp.ns) ? it - tp.ns : 0;
-            for (uint32_t j = first; j < it; j++) {
+            const uint32_t first = n_it > static_cast<uint32_t>(tp.ns) ? n_it - tp.ns : 0;
+            for (uint32_t j = first; j < n_it; j++) {
                 const uint64_t t0 = global_ns();
                 while (!mbar_try_wait(&bars->full[j % tp.ns], (j / tp.ns) & 1))
                     if (global_ns() - t0 > WAIT_NS) break;
@@ -115,20 +155,45 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
     }
 
     if (warp == TMA_REDUCER) {
-        // ---- reducer: adds a block's sixteen partials (fixed order), epilogue, store ----------------------------
+        // ---- reducer: adds a block's partials (fixed order), epilogue, store -----------------------------------
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         uint32_t bi = 0;
         const int per_tok = p.split << gsh;
         for (int blk = blockIdx.x; blk < tp.n_blocks; blk += gridDim.x, bi++) {
-            const int slot = bi % TMA_SLOTS;
-            float* blockpart = part + static_cast<size_t>(slot) * (TMA_CONSUMERS * NP * 128);
-            mbar_wait_warp(&bars->part_full[slot], (bi / TMA_SLOTS) & 1, &bars->abort_flag, p.err);
+            const int slot = bi % tp.slots;
+            float* blockpart = part + static_cast<size_t>(slot) * (tp.ksplit * NP * 128);
+            mbar_wait_warp(&bars->part_full[slot], (bi / tp.slots) & 1, &bars->abort_flag, p.err);
+            if (lane == 0 && bi < 6) TTRACE(44 + 2 * bi);
+            if (tp.rowsum) {
+                // single token: every consumer warp left its sixteen row sums; add them in warp order
+                const float* rs = part + static_cast<size_t>(slot) * (tp.ksplit * 16);
+                const int r = lane & 15;
+                float v = 0.0f;
+#pragma unroll
+                for (int wv = 0; wv < NC; wv++) if (wv < tp.ksplit) v += rs[wv * 16 + r];
+                const int row = blk * 16 + r;
+                if (lane < 16 && row < q.total_rows) {
+                    int pr = row, pi = 0;
+                    if (q.n_parts > 1 && pr >= q.part[0].rows) {
+                        pr -= q.part[0].rows; pi = 1;
+                        if (q.n_parts > 2 && pr >= q.part[1].rows) { pr -= q.part[1].rows; pi = 2; }
+                    }
+                    if (q.has_bias) v += load_scalar(q.part[pi].bias, q.bias_dtype, pr);
+                    if (q.e != nullptr) v = act_mul(q.act, v, __ldg(q.e + row));
+                    store_scalar(q.y, q.y_dtype, row, v);
+                }
+                __syncwarp();
+                if (lane == 0 && bi < 6) TTRACE(45 + 2 * bi);
+                if (lane == 0) mbar_arrive(&bars->part_empty[slot]);
+                continue;
+            }
             // stage 1: entry-wise sum over the consumer warps, four entries per lane per pass
             float4 acc[NP];
 #pragma unroll
             for (int ps = 0; ps < NP; ps++) {
                 acc[ps] = *reinterpret_cast<const float4*>(blockpart + ps * 128 + lane * 4);
-#pragma unroll
-                for (int wv = 1; wv < TMA_CONSUMERS; wv++) {
+#pragma unroll 4
+                for (int wv = 1; wv < tp.ksplit; wv++) {
                     const float4 o = *reinterpret_cast<const float4*>(blockpart + (wv * NP + ps) * 128 + lane * 4);
                     acc[ps].x += o.x; acc[ps].y += o.y; acc[ps].z += o.z; acc[ps].w += o.w;
                 }
@@ -162,6 +227,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                 }
             }
             __syncwarp();
+            if (lane == 0 && bi < 6) TTRACE(45 + 2 * bi);
             if (lane == 0) mbar_arrive(&bars->part_empty[slot]);
         }
         return;
@@ -173,9 +239,10 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
     constexpr int CTHREADS = TMA_CONSUMERS * 32;
 
     // stage the activations once per CTA (see qmv_mma.cuh for the layout)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     {
         const int cpr = K / 8;
-        for (int idx = ctid; idx < q.T * cpr; idx += CTHREADS) {
+        for (int idx = ctid; idx < ((MLXQ_ABLATE & 4) ? 0 : q.T * cpr); idx += CTHREADS) {
             const int tok = idx / cpr, k = (idx - tok * cpr) * 8;
             float v[8];
             if (q.x_dtype == DT_F16) XLoad<__half>::load8(reinterpret_cast<const __half*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
@@ -209,6 +276,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
     }
 
+    if (ctid == 0) TTRACE(16);
     // column bookkeeping, identical to qmv_mma_kernel
     const int run_grp_a = ((t * CL + mma_code_offset<BITS>(0)) >> gs_shift) & (G - 1);
     const int run_grp_b = ((t * CL + mma_code_offset<BITS>(NM / 2)) >> gs_shift) & (G - 1);
@@ -248,17 +316,48 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
 
     // this warp's steps of every block, cut at group boundaries
     const int nblk = steps_total >> spg_shift;
-    const int s_begin = ((nblk * warp) / TMA_CONSUMERS) << spg_shift;
-    const int s_end = ((nblk * (warp + 1)) / TMA_CONSUMERS) << spg_shift;
+    const int kw = warp % tp.ksplit, stream = warp / tp.ksplit, n_streams = TMA_CONSUMERS / tp.ksplit;
+    const int s_begin = ((nblk * kw) / tp.ksplit) << spg_shift;
+    const int s_end = ((nblk * (kw + 1)) / tp.ksplit) << spg_shift;
     const int gmin = (s_begin * KB) >> gs_shift;
     const int frag_off = g * static_cast<int>(row_bytes) + t * LB;       // row g of a half block, this lane's run
+    const __half* zeros = reinterpret_cast<const __half*>(smem_tma + tp.off_zero);
 
-    uint32_t it = 0, bi = 0;
-    for (int blk = blockIdx.x; blk < tp.n_blocks; blk += gridDim.x, bi++, it += 2) {
+    // Most calls drain once per block, after the warp's last step: everything about that drain but the block's
+    // scale rows is then the same for every block and is worked out here, once.
+    int n_drains = 0;
+    for (int s = s_begin; s < s_end; s++)
+        if (((s + 1) & ((1 << spg_shift) - 1)) == 0 && ((((s >> spg_shift) & cyc_mask) == cyc_mask) || s + 1 == s_end)) n_drains++;
+    bool f_ok = false;
+    int f_soff = 0;
+    float2 f_xv = make_float2(0.0f, 0.0f);
+    bool lane_fast = NP == 1 && pair16 && n_drains == 1;
+    {
+        const int s = s_end - 1, gblock = s >> spg_shift, cyc_s = gblock & cyc_mask;
+        const int gbase = (((gblock - cyc_s) << spg_shift) * KB) >> gs_shift;
+        const int glimit = ((s + 1) * KB) >> gs_shift;
+        const int g0 = gbase + c_goff[0][0], g1 = gbase + c_goff[0][1];
+        const bool ok0 = c_xc[0][0] >= 0 && g0 >= gmin && g0 < glimit;
+        const bool ok1 = c_xc[0][1] >= 0 && g1 >= gmin && g1 < glimit;
+        // a lane with one live column of its pair needs the general path: the whole warp stays on one path
+        lane_fast = lane_fast && ok0 == ok1;
+        f_ok = lane_fast && ok0;
+        if (f_ok) {
+            f_soff = tp.w_bytes + 2 * (g * groups + g0);
+            f_xv = *reinterpret_cast<const float2*>(xsum + c_xc[0][0] * groups + g0);
+        }
+    }
+    const bool fast_drain = __all_sync(0xffffffffu, lane_fast);
+    f_ok = f_ok && fast_drain;
+
+    if (ctid == 0) TTRACE(17);
+    // the CTA's blocks are dealt to the consumer groups in turn: group `stream` takes blocks stream, stream + n_streams, ...
+    for (uint32_t bi = stream; blockIdx.x + static_cast<long long>(bi) * gridDim.x < tp.n_blocks; bi += n_streams) {
+        const uint32_t it = 2 * bi;
         const int st0 = it % tp.ns, st1 = (it + 1) % tp.ns;
         const uint8_t* half0 = stages + static_cast<size_t>(st0) * tp.stage_bytes;   // rows 0..7: weights | scales | biases
         const uint8_t* half1 = stages + static_cast<size_t>(st1) * tp.stage_bytes;   // rows 8..15
-        constexpr int NCH = NP >= 4 ? 1 : 4 / NP;          // independent accumulator chains per pass
+        constexpr int NCH = NP >= 4 ? 1 : 4 / NP;          // independent accumulator chains per pass (eight were no faster)
         float yacc[NP][4], c[NP][NCH][4];
 #pragma unroll
         for (int ps = 0; ps < NP; ps++)
@@ -268,14 +367,23 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
 #pragma unroll
                 for (int k = 0; k < NCH; k++) c[ps][k][i] = 0.0f;
             }
+        // A stage's previous use may have gone to another consumer group, and bulk copies do not land in
+        // order: make sure that use has completed first, or its still-open phase would read as this one's
+        // parity.  (Uses two ring turns back are complete: this group's last block needed them released.)
+        if (n_streams > 1 && it >= static_cast<uint32_t>(tp.ns)) mbar_wait_warp(&bars->full[st0], ((it / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
+        if (n_streams > 1 && it + 1 >= static_cast<uint32_t>(tp.ns)) mbar_wait_warp(&bars->full[st1], (((it + 1) / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
         mbar_wait_warp(&bars->full[st0], (it / tp.ns) & 1, &bars->abort_flag, p.err);
         mbar_wait_warp(&bars->full[st1], ((it + 1) / tp.ns) & 1, &bars->abort_flag, p.err);
+        if (kw == 0 && lane == 0 && bi < 6) TTRACE(20 + 4 * bi);
 
         const uint8_t* f0 = half0 + frag_off + s_begin * (4 * LB);
         const uint8_t* f1 = half1 + frag_off + s_begin * (4 * LB);
-        for (int s = s_begin; s < s_end; s++, f0 += 4 * LB, f1 += 4 * LB) {
+        for (int s = s_begin; s < ((MLXQ_ABLATE & 2) ? s_begin : s_end); s++, f0 += 4 * LB, f1 += 4 * LB) {
             uint32_t w[2][NW];
-            if constexpr (LB == 16) {
+            if constexpr ((MLXQ_ABLATE & 32) != 0) {
+#pragma unroll
+                for (int i = 0; i < NW; i++) { w[0][i] = (s + i) * 0x01010101u + lane; w[1][i] = (s - i) * 0x01010101u + lane; }
+            } else if constexpr (LB == 16) {
                 const uint4 v0 = *reinterpret_cast<const uint4*>(f0), v1 = *reinterpret_cast<const uint4*>(f1);
                 w[0][0] = v0.x; w[0][1] = v0.y; w[0][2] = v0.z; w[0][3] = v0.w;
                 w[1][0] = v1.x; w[1][1] = v1.y; w[1][2] = v1.z; w[1][3] = v1.w;
@@ -290,6 +398,16 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
             const int gblock = s >> spg_shift;
             const int cyc_s = gblock & cyc_mask;
             const int koff = s * KB;
+            // lanes whose accumulator column belongs to another group (or cycle) multiply by zeros: they read
+            // them from a zeroed patch of shared memory, so the loads need no branch
+            const __half* pa[NP];
+            const __half* pb[NP];
+#pragma unroll
+            for (int ps = 0; ps < NP; ps++) {
+                const bool on = b_cyc[ps] == cyc_s;
+                pa[ps] = (keep_a[ps] && on) ? bptr[ps] + koff : zeros;
+                pb[ps] = (keep_b[ps] && on) ? bptr[ps] + koff : zeros;
+            }
 #pragma unroll
             for (int j = 0; j < NM; j += 2) {
                 uint32_t a00, a01, a02, a03, a10, a11, a12, a13;
@@ -299,14 +417,20 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                 a_regs<BITS>(w[1], j + 1, a11, a13);
 #pragma unroll
                 for (int ps = 0; ps < NP; ps++) {
-                    const bool keep = (j < NM / 2 ? keep_a[ps] : keep_b[ps]) && b_cyc[ps] == cyc_s;
-                    uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-                    if (keep) bv = *reinterpret_cast<const uint4*>(bptr[ps] + koff + 4 * j);
+                    uint4 bv;
+                    if (MLXQ_ABLATE & 16) bv = make_uint4(0x3c003c00u, 0x3c003c00u, 0x3c003c00u + s, 0x3c003c00u);
+                    else bv = *reinterpret_cast<const uint4*>((j < NM / 2 ? pa[ps] : pb[ps]) + 4 * j);
+                    if (MLXQ_ABLATE & 64) {
+                        c[ps][(j / 2) % NCH][0] += __uint_as_float((a00 ^ a01 ^ a02 ^ a03) + bv.x + bv.y);
+                        c[ps][(j / 2 + (NCH > 1 ? NCH / 2 : 0)) % NCH][1] += __uint_as_float((a10 ^ a11 ^ a12 ^ a13) + bv.z + bv.w);
+                        continue;
+                    }
                     mma16816(c[ps][(j / 2) % NCH], a00, a01, a02, a03, bv.x, bv.y);
                     mma16816(c[ps][(j / 2 + (NCH > 1 ? NCH / 2 : 0)) % NCH], a10, a11, a12, a13, bv.z, bv.w);
                 }
             }
-            if (((s + 1) & ((1 << spg_shift) - 1)) == 0 && (cyc_s == cyc_mask || s + 1 == s_end)) {
+            if (kw == 0 && lane == 0 && bi == 0 && s - s_begin < 6) TTRACE(56 + (s - s_begin));
+            if (!(MLXQ_ABLATE & 1) && ((s + 1) & ((1 << spg_shift) - 1)) == 0 && (cyc_s == cyc_mask || s + 1 == s_end)) {
                 // end of a group block that closes the cycle (or the warp's range): scale and bias in fp32
                 const int gbase = (((gblock - cyc_s) << spg_shift) * KB) >> gs_shift;
                 const int glimit = ((s + 1) * KB) >> gs_shift;
@@ -320,6 +444,32 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                         for (int k = 1; k < NCH; k++) cs[i] += c[ps][k][i];
 #pragma unroll
                         for (int k = 0; k < NCH; k++) c[ps][k][i] = 0.0f;
+                    }
+                    if (MLXQ_ABLATE & 8) {          // timing aid: keep the MMAs alive, leave out the scale / bias work
+#pragma unroll
+                        for (int i = 0; i < 4; i++) yacc[ps][i] += cs[i];
+                        continue;
+                    }
+                    if (fast_drain) {
+                        if (f_ok) {
+#pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                const uint8_t* rows = (h ? half1 : half0) + f_soff;
+                                const uint32_t su = *reinterpret_cast<const uint32_t*>(rows);
+                                const uint32_t bu = *reinterpret_cast<const uint32_t*>(rows + tp.s_bytes);
+                                float2 sf, bf;
+                                if (q.s_dtype == DT_F16) {
+                                    sf = __half22float2(*reinterpret_cast<const __half2*>(&su));
+                                    bf = __half22float2(*reinterpret_cast<const __half2*>(&bu));
+                                } else {
+                                    sf = make_float2(__uint_as_float(su << 16), __uint_as_float(su & 0xFFFF0000u));
+                                    bf = make_float2(__uint_as_float(bu << 16), __uint_as_float(bu & 0xFFFF0000u));
+                                }
+                                yacc[ps][2 * h] += fmaf(bf.x, f_xv.x, sf.x * 16777216.0f * cs[2 * h]);
+                                yacc[ps][2 * h + 1] += fmaf(bf.y, f_xv.y, sf.y * 16777216.0f * cs[2 * h + 1]);
+                            }
+                        }
+                        continue;
                     }
                     const int g0 = gbase + c_goff[ps][0], g1 = gbase + c_goff[ps][1];
                     const bool ok0 = c_xc[ps][0] >= 0 && g0 >= gmin && g0 < glimit;
@@ -359,26 +509,37 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                 }
             }
         }
+        if (kw == 0 && lane == 0 && bi < 6) TTRACE(21 + 4 * bi);
         // both half blocks are consumed (weights in registers, scales applied): hand them back
         __syncwarp();
         if (lane == 0) { mbar_arrive(&bars->empty[st0]); mbar_arrive(&bars->empty[st1]); }
 
         // deliver the partial sums to the reducer
-        const int slot = bi % TMA_SLOTS;
-        if (bi >= TMA_SLOTS) mbar_wait_warp(&bars->part_empty[slot], ((bi / TMA_SLOTS) - 1) & 1, &bars->abort_flag, p.err);
-        float* mine = part + (static_cast<size_t>(slot) * TMA_CONSUMERS + warp) * (NP * 128);
+        const int slot = bi % tp.slots;
+        if (bi >= static_cast<uint32_t>(tp.slots)) mbar_wait_warp(&bars->part_empty[slot], ((bi / tp.slots) - 1) & 1, &bars->abort_flag, p.err);
+        if (tp.rowsum) {
+            // one token: the eight accumulator columns of a row all belong to it -- add them across the quad
+            float lo = yacc[0][0] + yacc[0][1], hi = yacc[0][2] + yacc[0][3];
+            lo += __shfl_xor_sync(0xffffffffu, lo, 1); hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+            lo += __shfl_xor_sync(0xffffffffu, lo, 2); hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+            float* mine = part + (static_cast<size_t>(slot) * tp.ksplit + kw) * 16;
+            if (t == 0) { mine[g] = lo; mine[g + 8] = hi; }
+        } else {
+            float* mine = part + (static_cast<size_t>(slot) * tp.ksplit + kw) * (NP * 128);
 #pragma unroll
-        for (int ps = 0; ps < NP; ps++)
+            for (int ps = 0; ps < NP; ps++)
 #pragma unroll
-            for (int i = 0; i < 4; i++)
-                mine[(ps * 16 + g + 8 * (i >> 1)) * 8 + 2 * t + (i & 1)] = yacc[ps][i];
+                for (int i = 0; i < 4; i++)
+                    mine[(ps * 16 + g + 8 * (i >> 1)) * 8 + 2 * t + (i & 1)] = yacc[ps][i];
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->part_full[slot]);       // release semantics: the stores above are visible
+        if (kw == 0 && lane == 0 && bi < 6) TTRACE(22 + 4 * bi);
     }
 }
 
 // Plans the shared-memory layout for a call; returns the bytes needed, 0 when the call does not fit.
-size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, TmaPlan& tp);
-cudaError_t launch_qmv_tma(int bits, const MmaParams& p, const TmaPlan& tp, size_t smem, int sms, cudaStream_t st);
+size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, int sms, TmaPlan& tp);
+cudaError_t launch_qmv_tma(int bits, const MmaParams& p, const TmaPlan& tp, size_t smem, cudaStream_t st);
 
 }  // namespace mlxq
