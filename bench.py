@@ -246,16 +246,28 @@ def run_ours(args):
     y_host = torch.empty((LAYERS, total_rows), dtype=torch.float32).pin_memory()
     stream = torch.cuda.current_stream()
 
-    def step():
+    fused = comm is not None and args.gather == "fused"
+    if fused:
+        comm.window(((total_rows * 4 + 255) // 256) * 256)      # collective: the peer-mapped gather windows
+
+    def step(keep_outputs=False):
         for i, lin in enumerate(layers):
-            if comm is not None:
+            if fused:
+                # the decode kernel stores its rows into every rank's window itself; no collective kernel
+                # (each call waits for the peers' rows of the one before it, the explicit wait covers the last)
+                out = comm.forwardGatherFused(lin, stream, x_dev, K_COLS, 1, wait=keep_outputs)
+                if keep_outputs:
+                    y_dev[i].copy_(out[0], non_blocking=True)
+            elif comm is not None:
                 comm.forwardGather(lin, stream, x_dev, K_COLS, y_dev[i], total_rows, 1)
             else:
                 lin.encode(stream, x_dev, K_COLS, y_dev[i], O_ROWS, 1)
+        if fused and not keep_outputs:
+            comm.wait(stream)
 
     def step_e2e():
         x_dev.copy_(x_host, non_blocking=True)
-        step()
+        step(keep_outputs=True)
         y_host.copy_(y_dev, non_blocking=True)
         stream.synchronize()
 
@@ -316,7 +328,8 @@ def run_ours(args):
                                    f"{LAYERS} distinct weight sets per step ({LAYERS * per_launch / 1e6:.0f} MB > L2)",
                        "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS, "group_size": GS, "batch": 1,
                        "launches_per_step": LAYERS, "l2": "inputs larger than L2",
-                       "parallelism": f"row-shard x{world} + all-gather" if world > 1 else "single GPU"},
+                       "parallelism": (f"row-shard x{world} + " + ("peer-store gather fused into the kernel" if fused else
+                                                                   "ncclAllGather")) if world > 1 else "single GPU"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
                     "d2h_bytes_per_step": int(y_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,
@@ -347,6 +360,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length (0 = skip)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM probe")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: rows stored into the peers' windows by the decode kernel (fused) or ncclAllGather after it")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight sets per step (default 16)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -105,6 +105,8 @@ MLXQ_API int mlxq_linear_bits(mlxq_linear_t h);
 MLXQ_API int mlxq_linear_group_size(mlxq_linear_t h);
 /* First global output row of a shard (0 for an unsharded layer). */
 MLXQ_API int64_t mlxq_linear_row_offset(mlxq_linear_t h);
+/* Rows of the whole layer: out_dim for an unsharded handle, the sum over the shards otherwise. */
+MLXQ_API int64_t mlxq_linear_total_rows(mlxq_linear_t h);
 
 /* ---- encode: Linear.encode, Transformer.swift:272-315 ---------------------------------------------- */
 
@@ -195,6 +197,29 @@ MLXQ_API int mlxq_comm_size(mlxq_comm_t c);
  * collective is issued. */
 MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t stream, const void* x,
                                         int x_dtype, int64_t x_stride, float* y, int64_t y_stride, int64_t T);
+
+/* Fused shard forward + gather (no counterpart in the reference, which runs on one GPU).  The decode kernel
+ * itself stores every output row into the gather window of every rank (peer memory over NVLink) and raises
+ * a flag on every rank when its rows are out, so no collective kernel follows it.
+ *
+ * mlxq_comm_window allocates the window: two buffers of `bytes` each (a positive multiple of 256; at least
+ * T * total rows * 4), mapped into the other ranks through CUDA IPC.  It is a collective: every rank calls
+ * it, once per communicator, with the same size, with no work pending on the device.
+ *
+ * mlxq_linear_forward_gather_fused enqueues the call and returns in *y_full the device address of the
+ * gathered output, fp32 [T, total rows] (row stride = total rows).  The kernel does not wait for the other
+ * ranks: the rows are complete in `stream` order once the next fused call of the communicator has begun
+ * (it waits for the peers before it reads its activations, while its weight copies are already in flight)
+ * or after mlxq_comm_wait(c, stream), which enqueues that wait alone; any other reader needs the latter.
+ * The address stays valid until the second-next fused call (calls alternate between the two buffers).
+ * Every rank must issue the same sequence of fused calls.  Only shapes the persistent decode kernel serves
+ * (T <= 16, the usual alignment) are accepted; others return MLXQ_UNSUPPORTED and leave the communicator
+ * untouched -- use mlxq_linear_forward_gather for those.  A wait for a peer gives up after two seconds:
+ * the result is then incomplete and mlxq_stream_status reports MLXQ_TIMEOUT. */
+MLXQ_API int mlxq_comm_window(mlxq_comm_t c, size_t bytes);
+MLXQ_API int mlxq_linear_forward_gather_fused(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t stream, const void* x,
+                                              int x_dtype, int64_t x_stride, int64_t T, float** y_full);
+MLXQ_API int mlxq_comm_wait(mlxq_comm_t c, mlxq_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -48,6 +48,7 @@ SIGNATURES = {
     "mlxq_linear_bits": (C.c_int, [C.c_void_p]),
     "mlxq_linear_group_size": (C.c_int, [C.c_void_p]),
     "mlxq_linear_row_offset": (C.c_int64, [C.c_void_p]),
+    "mlxq_linear_total_rows": (C.c_int64, [C.c_void_p]),
     "mlxq_linear_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int,
                                       C.c_int64, C.c_int64]),
     "mlxq_linear_forward_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p,
@@ -73,6 +74,10 @@ SIGNATURES = {
     "mlxq_comm_size": (C.c_int, [C.c_void_p]),
     "mlxq_linear_forward_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
                                              C.c_void_p, C.c_int64, C.c_int64]),
+    "mlxq_comm_window": (C.c_int, [C.c_void_p, C.c_size_t]),
+    "mlxq_comm_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mlxq_linear_forward_gather_fused": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
+                                                   C.c_int64, C.POINTER(C.c_void_p)]),
 }
 
 _lib = None

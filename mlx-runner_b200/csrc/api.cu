@@ -220,9 +220,11 @@ static size_t mma_plan(const mlxq_linear_t* parts, int n, int x_dtype, int64_t T
 }
 
 static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const void* x, int x_dtype, int64_t x_stride,
-                   void* y, int y_dtype, int64_t y_stride, int64_t T, const float* e, int act) {
+                   void* y, int y_dtype, int64_t y_stride, int64_t T, const float* e, int act,
+                   const PeerGather* peer = nullptr) {
     QmvParams p;
     fill_qmv(p, parts, n);
+    if (peer) p.peer = *peer; else p.peer.n = 0;
     p.x_dtype = x_dtype;
     p.y_dtype = y_dtype;
     p.x_stride = x_stride;
@@ -240,11 +242,13 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         const char* mode = getenv("MLXQ_DECODE");
         TmaPlan tp;
         const size_t tsmem = (mode && strcmp(mode, "mma") == 0) || !mp.err ? 0 : qmv_tma_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), tp);
+        if (peer && !tsmem) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
         cudaError_t err = tsmem ? launch_qmv_tma(parts[0]->bits, mp, tp, tsmem, st)
                                 : launch_qmv_mma(parts[0]->bits, mp, smem, st);
         if (err != cudaSuccess) return cuda_fail(err, "qmv (tensor-core) launch");
         return MLXQ_OK;
     }
+    if (peer) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
     // gridDim.y carries token tiles of four; walk very long batches in slices.
     const int64_t slice = 4 * 65535;
     for (int64_t t0 = 0; t0 < T; t0 += slice) {
@@ -276,7 +280,7 @@ static int gemm_tile_for(const mlxq_linear* h, int x_dtype, int64_t x_stride, co
 }
 
 int forward_impl(mlxq_linear_t h, cudaStream_t st, const void* x, int x_dtype, int64_t x_stride, void* y, int y_dtype,
-                 int64_t y_stride, int64_t T) {
+                 int64_t y_stride, int64_t T, const PeerGather* peer) {
     if (!h) return fail(MLXQ_INVALID_ARGUMENT, "null layer");
     if (T < 1) return fail(MLXQ_INVALID_ARGUMENT, "T = %lld", (long long)T);
     if (int rc = check_x(x, x_dtype, x_stride, h->in_dim, T)) return rc;
@@ -285,6 +289,7 @@ int forward_impl(mlxq_linear_t h, cudaStream_t st, const void* x, int x_dtype, i
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
     if (gemm_tile_for(h, x_dtype, x_stride, x, T) > 0) {
+        if (peer) return fail(MLXQ_UNSUPPORTED, "batches of %lld tokens take the GEMM: no fused gather", (long long)T);
         GemmCall c;
         c.x = x; c.x_dtype = x_dtype; c.x_stride = x_stride; c.y = y; c.y_dtype = y_dtype; c.y_stride = y_stride; c.T = T;
         c.err = device_error_word(h->device);
@@ -293,7 +298,7 @@ int forward_impl(mlxq_linear_t h, cudaStream_t st, const void* x, int x_dtype, i
         if (err != cudaSuccess) return fail(MLXQ_GPU_FAILURE, "qgemm launch: %s (%s)", cudaGetErrorString(err), why);
         return MLXQ_OK;
     }
-    return run_qmv(&h, 1, st, x, x_dtype, x_stride, y, y_dtype, y_stride, T, nullptr, 0);
+    return run_qmv(&h, 1, st, x, x_dtype, x_stride, y, y_dtype, y_stride, T, nullptr, 0, peer);
 }
 
 }  // namespace mlxq
@@ -375,6 +380,7 @@ int64_t mlxq_linear_out_dim(mlxq_linear_t h) { return h ? h->out_dim : 0; }
 int mlxq_linear_bits(mlxq_linear_t h) { return h ? h->bits : 0; }
 int mlxq_linear_group_size(mlxq_linear_t h) { return h ? h->gs : 0; }
 int64_t mlxq_linear_row_offset(mlxq_linear_t h) { return h ? h->row_offset : 0; }
+int64_t mlxq_linear_total_rows(mlxq_linear_t h) { return h ? h->total_out : 0; }
 
 int mlxq_linear_forward(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, int64_t x_stride, void* y,
                         int y_dtype, int64_t y_stride, int64_t T) {

@@ -6,6 +6,8 @@
 
 #include <string>
 
+#include "peer_gather.h"
+
 // The layer handle behind mlxq_linear_t: borrowed device pointers plus the facts derived from shapes.
 struct mlxq_linear {
     const uint8_t* w;
@@ -30,7 +32,9 @@ int fail(int status, const char* fmt, ...) __attribute__((format(printf, 2, 3)))
 int cuda_fail(cudaError_t e, const char* what);
 // Device address of the per-device error word (nullptr if the device cannot be selected).
 unsigned* device_error_word(int device);
+// `peer` (optional): also store the rows into the peers' windows and run the flag hand-shake; only the persistent
+// decode kernel can do that, other paths return MLXQ_UNSUPPORTED when it is given.
 int forward_impl(mlxq_linear* h, cudaStream_t st, const void* x, int x_dtype, int64_t x_stride, void* y, int y_dtype,
-                 int64_t y_stride, int64_t T);
+                 int64_t y_stride, int64_t T, const PeerGather* peer = nullptr);
 
 }  // namespace mlxq

@@ -58,10 +58,59 @@ int nccl_fail(ncclResult_t r, const char* what) {
 
 }  // namespace
 
+// The gather window: two buffers of `bytes` each (calls alternate between them, so a rank that runs ahead
+// never overwrites rows a slower rank's next kernels still read), mapped into every peer through CUDA IPC,
+// plus one flag word per rank and a CTA counter.
+struct GatherWindow {
+    char* local = nullptr;
+    char* peer[mlxq::MAX_PEERS + 1] = {};        // by rank; [rank] == local
+    unsigned* flags = nullptr;                   // this rank's flag array
+    unsigned* peer_flags[mlxq::MAX_PEERS + 1] = {};
+    unsigned* counter = nullptr;
+    size_t bytes = 0;
+    unsigned epoch = 0;
+};
+
 struct mlxq_comm {
     ncclComm_t comm;
     int rank, size, device;
+    GatherWindow win;
 };
+
+namespace {
+
+// One warp: lane p waits (bounded, two seconds) until peer p's flag in this rank's array has reached `epoch`.
+__global__ void gather_wait_kernel(const unsigned* my_flags, int rank, int nranks, unsigned epoch, unsigned* err) {
+    const int p = threadIdx.x;
+    if (p >= nranks || p == rank) return;
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flags + p) : "memory");
+        if (static_cast<int>(seen - epoch) >= 0) return;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > 2000000000ull) { atomicOr(err, 2u | 8u); return; }     // ERR_WAIT_TIMEOUT | ERR_PEER_FLAG
+    }
+}
+
+struct IpcPair {
+    cudaIpcMemHandle_t window, flags;
+};
+
+void close_window(mlxq_comm* c) {
+    GatherWindow& w = c->win;
+    for (int r = 0; r < c->size && r <= mlxq::MAX_PEERS; r++) {
+        if (r == c->rank) continue;
+        if (w.peer[r]) cudaIpcCloseMemHandle(w.peer[r]);
+        if (w.peer_flags[r]) cudaIpcCloseMemHandle(w.peer_flags[r]);
+    }
+    if (w.local) cudaFree(w.local);
+    if (w.flags) cudaFree(w.flags);
+    w = GatherWindow();
+}
+
+}  // namespace
 
 static_assert(sizeof(ncclUniqueId) == MLXQ_COMM_ID_BYTES, "rendezvous token size");
 
@@ -81,7 +130,7 @@ int mlxq_comm_create(const uint8_t id[MLXQ_COMM_ID_BYTES], int rank, int nranks,
     if (!out) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "null argument");
     *out = nullptr;
     if (nranks < 1 || rank < 0 || rank >= nranks) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "rank %d of %d", rank, nranks);
-    auto* c = new (std::nothrow) mlxq_comm{nullptr, rank, nranks, device};
+    auto* c = new (std::nothrow) mlxq_comm{nullptr, rank, nranks, device, GatherWindow()};
     if (!c) return mlxq::fail(MLXQ_OUT_OF_MEMORY, "communicator allocation");
     if (nranks > 1) {
         if (!id) { delete c; return mlxq::fail(MLXQ_INVALID_ARGUMENT, "null id"); }
@@ -99,6 +148,7 @@ int mlxq_comm_create(const uint8_t id[MLXQ_COMM_ID_BYTES], int rank, int nranks,
 
 void mlxq_comm_destroy(mlxq_comm_t c) {
     if (!c) return;
+    close_window(c);
     if (c->comm) nccl().CommDestroy(c->comm);
     delete c;
 }
@@ -129,6 +179,103 @@ int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t str
     r = n.GroupEnd();
     if (r != ncclSuccess) return nccl_fail(r, "ncclGroupEnd");
     return MLXQ_OK;
+}
+
+int mlxq_comm_window(mlxq_comm_t c, size_t bytes) {
+    if (!c) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "null communicator");
+    if (bytes == 0 || bytes % 256 != 0) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "window size %zu is not a positive multiple of 256", bytes);
+    if (c->size > mlxq::MAX_PEERS + 1) return mlxq::fail(MLXQ_UNSUPPORTED, "%d ranks: the fused gather serves up to %d", c->size, mlxq::MAX_PEERS + 1);
+    if (c->win.local) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "the communicator already has a window");
+    cudaError_t e = cudaSetDevice(c->device);
+    if (e != cudaSuccess) return mlxq::cuda_fail(e, "cudaSetDevice");
+    GatherWindow& w = c->win;
+    // flags: one word per rank, then the CTA counter
+    if ((e = cudaMalloc(&w.local, 2 * bytes)) != cudaSuccess) return mlxq::cuda_fail(e, "window allocation");
+    if ((e = cudaMalloc(&w.flags, 256)) != cudaSuccess) { close_window(c); return mlxq::cuda_fail(e, "flag allocation"); }
+    cudaMemset(w.local, 0, 2 * bytes);
+    cudaMemset(w.flags, 0, 256);
+    w.counter = w.flags + 32;
+    w.bytes = bytes;
+    w.peer[c->rank] = w.local;
+    w.peer_flags[c->rank] = w.flags;
+    if (c->size == 1) return cudaDeviceSynchronize() == cudaSuccess ? MLXQ_OK : mlxq::fail(MLXQ_GPU_FAILURE, "window set-up");
+    // exchange the IPC handles with an all-gather on the communicator itself
+    IpcPair mine;
+    if ((e = cudaIpcGetMemHandle(&mine.window, w.local)) != cudaSuccess || (e = cudaIpcGetMemHandle(&mine.flags, w.flags)) != cudaSuccess) {
+        close_window(c);
+        return mlxq::cuda_fail(e, "cudaIpcGetMemHandle");
+    }
+    IpcPair* dev = nullptr;
+    IpcPair all[mlxq::MAX_PEERS + 1];
+    if ((e = cudaMalloc(&dev, sizeof(IpcPair) * (c->size + 1))) != cudaSuccess) { close_window(c); return mlxq::cuda_fail(e, "handle staging"); }
+    cudaMemcpy(dev + c->size, &mine, sizeof mine, cudaMemcpyHostToDevice);
+    ncclResult_t r = nccl().AllGather(dev + c->size, dev, sizeof(IpcPair), /*ncclInt8*/ 0, c->comm, nullptr);
+    if (r == ncclSuccess) e = cudaStreamSynchronize(nullptr);
+    if (r == ncclSuccess && e == cudaSuccess) e = cudaMemcpy(all, dev, sizeof(IpcPair) * c->size, cudaMemcpyDeviceToHost);
+    cudaFree(dev);
+    if (r != ncclSuccess) { close_window(c); return nccl_fail(r, "handle exchange"); }
+    if (e != cudaSuccess) { close_window(c); return mlxq::cuda_fail(e, "handle exchange"); }
+    for (int p = 0; p < c->size; p++) {
+        if (p == c->rank) continue;
+        void* a = nullptr;
+        void* b = nullptr;
+        if ((e = cudaIpcOpenMemHandle(&a, all[p].window, cudaIpcMemLazyEnablePeerAccess)) != cudaSuccess ||
+            (e = cudaIpcOpenMemHandle(&b, all[p].flags, cudaIpcMemLazyEnablePeerAccess)) != cudaSuccess) {
+            if (a) cudaIpcCloseMemHandle(a);
+            close_window(c);
+            return mlxq::cuda_fail(e, "cudaIpcOpenMemHandle (peer window)");
+        }
+        w.peer[p] = static_cast<char*>(a);
+        w.peer_flags[p] = static_cast<unsigned*>(b);
+    }
+    return MLXQ_OK;
+}
+
+int mlxq_linear_forward_gather_fused(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t stream, const void* x, int x_dtype,
+                                     int64_t x_stride, int64_t T, float** y_full) {
+    if (!h || !c || !y_full) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    *y_full = nullptr;
+    if (h->shard_count != c->size || h->shard_rank != c->rank)
+        return mlxq::fail(MLXQ_INVALID_ARGUMENT, "layer is shard %d of %d but the communicator is rank %d of %d",
+                          h->shard_rank, h->shard_count, c->rank, c->size);
+    GatherWindow& w = c->win;
+    if (!w.local) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "the communicator has no window (mlxq_comm_window)");
+    if (T < 1 || static_cast<unsigned long long>(T) * h->total_out * 4ull > w.bytes)
+        return mlxq::fail(MLXQ_INVALID_ARGUMENT, "%lld tokens x %lld rows do not fit the %zu-byte window", (long long)T, (long long)h->total_out, w.bytes);
+    const unsigned epoch = w.epoch + 1;
+    const size_t half = (epoch & 1u) * w.bytes;
+    float* y = reinterpret_cast<float*>(w.local + half);
+    mlxq::PeerGather pg = {};
+    pg.rank = c->rank;
+    pg.epoch = epoch;
+    pg.wait_epoch = w.epoch;          // the previous fused call: its rows may be this call's activations
+    pg.my_flags = w.flags;
+    pg.counter = w.counter;
+    for (int p = 0; p < c->size; p++) {
+        if (p == c->rank) continue;
+        pg.y[pg.n] = w.peer[p] + half + static_cast<size_t>(h->row_offset) * 4;
+        pg.flag[pg.n] = w.peer_flags[p];
+        pg.peer_rank[pg.n] = p;
+        pg.n++;
+    }
+    int rc = mlxq::forward_impl(h, static_cast<cudaStream_t>(stream), x, x_dtype, x_stride, y + h->row_offset, MLXQ_F32,
+                                h->total_out, T, c->size > 1 ? &pg : nullptr);
+    if (rc != MLXQ_OK) return rc;
+    w.epoch = epoch;          // only calls that were enqueued count: every rank takes the same decision for a shape
+    *y_full = y;
+    return MLXQ_OK;
+}
+
+int mlxq_comm_wait(mlxq_comm_t c, mlxq_stream_t stream) {
+    if (!c) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "null communicator");
+    if (c->size == 1 || !c->win.local || c->win.epoch == 0) return MLXQ_OK;
+    cudaError_t e = cudaSetDevice(c->device);
+    if (e != cudaSuccess) return mlxq::cuda_fail(e, "cudaSetDevice");
+    unsigned* err = mlxq::device_error_word(c->device);
+    if (!err) return mlxq::fail(MLXQ_GPU_FAILURE, "no error word on device %d", c->device);
+    gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->win.flags, c->rank, c->size, c->win.epoch, err);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? MLXQ_OK : mlxq::cuda_fail(e, "gather wait launch");
 }
 
 }  // extern "C"

@@ -12,7 +12,7 @@ namespace mlxq {
 enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
 
 // Device-side error word bits (one word per device, read by mlxq_stream_status).
-enum : unsigned { ERR_BAD_LOOKUP_ID = 1u, ERR_WAIT_TIMEOUT = 2u, ERR_GEMM_PIPELINE = 4u };
+enum : unsigned { ERR_BAD_LOOKUP_ID = 1u, ERR_WAIT_TIMEOUT = 2u, ERR_GEMM_PIPELINE = 4u, ERR_PEER_FLAG = 8u };
 
 __host__ __device__ inline int dtype_size(int dt) { return dt == DT_F32 ? 4 : 2; }
 

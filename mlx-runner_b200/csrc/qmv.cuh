@@ -14,6 +14,7 @@
 #pragma once
 
 #include "mlxq_device.cuh"
+#include "peer_gather.h"
 
 namespace mlxq {
 
@@ -40,6 +41,7 @@ struct QmvParams {
     int fast;           // rows and base pointers are 16-byte aligned: 128-bit loads allowed
     int seg32;          // gs % 32 == 0: one (scale, bias) per aligned 32-code segment
     int gs_shift;       // log2(gs) when gs is a power of two, else -1
+    PeerGather peer;    // sharded calls of the persistent decode kernel: peers that receive the rows too
 };
 
 template <int BITS> struct QmvUnit {

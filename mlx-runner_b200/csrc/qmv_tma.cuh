@@ -63,6 +63,18 @@ struct TmaBars {
     int abort_flag;
 };
 
+// Bounded wait until a peer's flag has reached `epoch` (flags only grow; the difference is taken signed so the
+// counter may wrap).  On time-out the error word is set and the caller carries on: the host discards the result.
+__device__ __forceinline__ void peer_flag_wait(const unsigned* flag, unsigned epoch, unsigned* err) {
+    const uint64_t t0 = global_ns();
+    for (;;) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+        if (static_cast<int>(seen - epoch) >= 0) return;
+        if (global_ns() - t0 > WAIT_NS) { atomicOr(err, ERR_WAIT_TIMEOUT | ERR_PEER_FLAG); return; }
+    }
+}
+
 template <int BITS, int NP, int NC>
 __global__ void __launch_bounds__((NC + 2) * 32, NC == 8 ? 2 : 1)
 qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
@@ -181,6 +193,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                     if (q.has_bias) v += load_scalar(q.part[pi].bias, q.bias_dtype, pr);
                     if (q.e != nullptr) v = act_mul(q.act, v, __ldg(q.e + row));
                     store_scalar(q.y, q.y_dtype, row, v);
+                    for (int pp = 0; pp < q.peer.n; pp++) store_scalar(q.peer.y[pp], q.y_dtype, row, v);
                 }
                 __syncwarp();
                 if (lane == 0 && bi < 6) TTRACE(45 + 2 * bi);
@@ -224,11 +237,29 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                     if (q.has_bias) v += load_scalar(q.part[pi].bias, q.bias_dtype, pr);
                     if (q.e != nullptr) v = act_mul(q.act, v, __ldg(q.e + row));
                     store_scalar(q.y, q.y_dtype, static_cast<size_t>(tok) * q.y_stride + row, v);
+                    for (int pp = 0; pp < q.peer.n; pp++)
+                        store_scalar(q.peer.y[pp], q.y_dtype, static_cast<size_t>(tok) * q.y_stride + row, v);
                 }
             }
             __syncwarp();
             if (lane == 0 && bi < 6) TTRACE(45 + 2 * bi);
             if (lane == 0) mbar_arrive(&bars->part_empty[slot]);
+        }
+        if (q.peer.n > 0) {
+            // Sharded call: this CTA's rows are on their way to every peer's window.  The CTA that finishes last
+            // publishes this rank's epoch in every peer's flag array.  Nobody waits here: the next call on the
+            // communicator (or mlxq_comm_wait) waits for the peers' flags before it reads the gathered rows,
+            // and by then its own weight copies are already in flight.
+            __threadfence_system();
+            __syncwarp();
+            unsigned last = 0;
+            if (lane == 0) last = atomicInc(q.peer.counter, gridDim.x - 1) == gridDim.x - 1 ? 1u : 0u;
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_system();
+                if (lane < q.peer.n)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(q.peer.flag[lane] + q.peer.rank), "r"(q.peer.epoch) : "memory");
+            }
         }
         return;
     }
@@ -240,6 +271,11 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
 
     // stage the activations once per CTA (see qmv_mma.cuh for the layout)
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (q.peer.n > 0 && q.peer.wait_epoch != 0) {
+        // the activations may be the previous sharded call's gathered output: every peer must have finished it
+        if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], q.peer.wait_epoch, p.err);
+        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
+    }
     {
         const int cpr = K / 8;
         for (int idx = ctid; idx < ((MLXQ_ABLATE & 4) ? 0 : q.T * cpr); idx += CTHREADS) {

@@ -214,6 +214,7 @@ class Linear:
         self.bits = int(lib.mlxq_linear_bits(h))
         self.groupSize = int(lib.mlxq_linear_group_size(h))
         self.rowOffset = int(lib.mlxq_linear_row_offset(h))
+        self.totalOut = int(lib.mlxq_linear_total_rows(h))
         self.description = f"q{self.bits}g{self.groupSize}"
 
     @classmethod
@@ -357,6 +358,15 @@ def streamStatus(stream=None, device: int = 0) -> None:
     check(L.load().mlxq_stream_status(_stream_handle(stream), device))
 
 
+class _DeviceArray:
+    """An fp32 device buffer owned by the library, exposed through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, shape, device: int):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+        self.device = device
+
+
 class Comm:
     """The communicator behind row-sharded layers: one process per GPU, NCCL all-gather of output slices."""
 
@@ -370,6 +380,7 @@ class Comm:
         h = C.c_void_p()
         check(lib.mlxq_comm_create(idbuf, rank, nranks, device, C.byref(h)))
         self._h, self.rank, self.size, self.device = h, rank, nranks, device
+        self._views = {}
 
     @staticmethod
     def uniqueId() -> bytes:
@@ -383,8 +394,36 @@ class Comm:
         check(L.load().mlxq_linear_forward_gather(layer._h, self._h, _stream_handle(stream), _ptr(x),
                                                   _act_dtype(x, xDtype), xStride, _ptr(y), yStride, T))
 
+    def window(self, nbytes: int) -> None:
+        """Collective: allocate this rank's gather window (two buffers of nbytes) and map the peers' windows."""
+        check(L.load().mlxq_comm_window(self._h, nbytes))
+
+    def forwardGatherFused(self, layer: Linear, stream, x, xStride: int, T: int, xDtype: Optional[int] = None,
+                           wait: bool = True):
+        """Shard matvec whose kernel stores its rows into every rank's window.  Returns the gathered output as
+        an fp32 CUDA tensor [T, total rows] that aliases the window: valid until the second-next fused call.
+        ``wait=False`` leaves out the wait for the peers' rows: right when the next thing in the stream is
+        another fused call (it waits itself) -- call ``wait(stream)`` before anything else reads the tensor."""
+        out = C.c_void_p()
+        check(L.load().mlxq_linear_forward_gather_fused(layer._h, self._h, _stream_handle(stream), _ptr(x),
+                                                        _act_dtype(x, xDtype), xStride, T, C.byref(out)))
+        if wait:
+            self.wait(stream)
+        key = (out.value, T, layer.totalOut)
+        view = self._views.get(key)
+        if view is None:                 # two addresses per shape: the views are made once
+            import torch
+            view = torch.as_tensor(_DeviceArray(out.value, (T, layer.totalOut), self.device), device=f"cuda:{self.device}")
+            self._views[key] = view
+        return view
+
+    def wait(self, stream) -> None:
+        """Enqueue the wait for every peer's rows of the last fused call."""
+        check(L.load().mlxq_comm_wait(self._h, _stream_handle(stream)))
+
     def close(self) -> None:
         h, self._h = self._h, None
+        self._views = {}
         if h:
             L.load().mlxq_comm_destroy(h)
 

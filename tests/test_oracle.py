@@ -149,3 +149,21 @@ def test_act_mul_values(oracle):
     from math import erf
     gelu_e = np.array([0.5 * a * (1 + erf(a / np.sqrt(2))) for a in g]) * u
     assert np.allclose(oracle.act_mul(2, g, u), gelu_e, atol=1e-6)
+
+
+def test_oracle_reproduces_the_committed_golden_cases(oracle):
+    # tests/golden/qlinear_cases.npz pins the oracle at the state that was checked against the reference's
+    # known-answer material: packing, unpacking and the dense double-accumulate reference, bit for bit
+    import golden_cases
+    cases = golden_cases.load()
+    assert len(cases) == 18
+    for c in cases:
+        assert np.array_equal(oracle.pack(c.q, c.bits), c.packed), c.name
+        assert np.array_equal(oracle.unpack(c.packed, c.K, c.bits), c.q), c.name
+        fx = oracle.QuantFixture(O=c.O, K=c.K, bits=c.bits, gs=c.gs, scale_type=c.sdt, with_bias=c.bias is not None, seed=c.seed)
+        assert np.array_equal(fx.scales_raw, c.scales) and np.array_equal(fx.biases_raw, c.biases), c.name
+        assert np.array_equal(fx.reference(c.x).view(np.uint32), c.y.view(np.uint32)), c.name
+        # the fused form the kernels implement (scale * sum(q x) + bias * sum(x)) agrees with it to 1e-3
+        y2 = oracle.qmatmul(c.packed, c.scales, c.biases, c.sdt, c.x, c.K, c.bits, c.gs,
+                            bias=None if c.bias is None else fx.bias)
+        assert oracle.max_rel_err(y2, c.y) < 1e-3, c.name

@@ -276,3 +276,18 @@ def test_baseline_shapes_against_oracle(mlxq, oracle):
             _, x = synth.make_activations(M, 4096, synth.F16, seed=M)
             ref = oracle.qmatmul(lay.packed, lay.scales_raw, lay.biases_raw, lay.scale_dtype, x, 4096, bits, gs)
             close(oracle, run(layer, x, M, x_dtype=1), ref, f"config 2 bits {bits} gs {gs} M {M}")
+
+
+def test_committed_golden_cases(mlxq, oracle):
+    # every bit width x group size of tests/golden/qlinear_cases.npz: codes bit-exact, outputs within 1e-3
+    import golden_cases
+    for c in golden_cases.load():
+        layer = DevLayer(mlxq, c.packed, c.scales, c.biases, c.sdt, c.K, bias_raw=c.bias, name=c.name)
+        codes = torch.full((c.O, c.K), 255, dtype=torch.uint8, device="cuda")
+        layer.linear.unpackCodes(None, codes)
+        torch.cuda.synchronize()
+        assert np.array_equal(codes.cpu().numpy(), c.q), c.name
+        for T in (1, c.T):
+            got = run(layer, c.x[:T], T)
+            assert oracle.max_rel_err(got, c.y[:T]) < 1e-3, f"{c.name} T={T}"
+    mlxq.streamStatus(None, 0)
