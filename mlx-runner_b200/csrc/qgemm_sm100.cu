@@ -64,11 +64,20 @@ constexpr int S_A = 4;                  // TMEM stages of the A operand
 constexpr int X_STAGE = BN * BK * 2;    // 16384 bytes
 constexpr int W_SLAB = BM * 128;        // 32768 bytes: 256 rows x 128 bytes, 128-byte swizzle
 constexpr int NUM_THREADS = 20 * 32;
-constexpr int W_PRODUCER = 2;           // warp that streams the packed weight slabs (warp 3 is idle)
+constexpr int W_PRODUCER = 2;           // warp that streams the packed weight slabs
+#ifndef MLXQ_MMA_WARP
+#define MLXQ_MMA_WARP 1
+#endif
+constexpr int MMA_WARP = MLXQ_MMA_WARP;  // warp whose lane 0 issues the MMAs; it also owns the tensor-memory allocation
 constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16;
 constexpr int TMEM_COLS = 512;
 constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
 constexpr int A_COL0 = 2 * BN;          // A ring: S_A stages x 2 halves x 32 columns
+// First tensor-memory column of the 16 columns (32 fp16) that one dequantising warp stores for ring stage `sa`,
+// row half `half`, K half `khalf`.
+__host__ __device__ constexpr uint32_t a_col(int sa, int half, int khalf) {
+    return A_COL0 + static_cast<uint32_t>((sa * 2 + half) * (BK / 2) + khalf * 16);
+}
 
 struct Barriers {
     uint64_t full_x[S_X];
@@ -132,7 +141,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -187,7 +196,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     if (global_ns() - t0 > WAIT_NS) break;
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == MMA_WARP) {
         // ---- MMA issuer ------------------------------------------------------------------------------------
         if (lane == 0) {
             uint32_t it = 0, tile_i = 0;
@@ -205,10 +214,9 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
                         const uint32_t d_addr = tmem + D_COL0 + half * BN;
-                        const uint32_t a_addr = tmem + A_COL0 + (sa * 2 + half) * (BK / 2);
 #pragma unroll
                         for (int kk = 0; kk < BK / 16; kk++)
-                            tc_mma_ts(d_addr, a_addr + kk * 8, bdesc + static_cast<uint64_t>(kk * 2), a.idesc, (ks | kk) != 0);
+                            tc_mma_ts(d_addr, tmem + a_col(sa, half, kk >> 1) + (kk & 1) * 8, bdesc + static_cast<uint64_t>(kk * 2), a.idesc, (ks | kk) != 0);
                     }
                     tc_commit(&bars->empty_x[s]);      // the activation tile of stage s is free again
                     tc_commit(&bars->empty_a[sa]);     // so is the A stage in tensor memory
@@ -342,23 +350,38 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 }
                 const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
                 uint32_t v[16];
+                // One decision per warp and stage, outside the unrolled loops: left per lane inside them, the
+                // compiler evaluated both dequant forms for every value (3x the half-precision FMAs).
+                if (__all_sync(0xffffffffu, small)) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    // nibbles (0,4), (1,5), (2,6), (3,7) of the word, each pair brought to bits 4..7 of its half
-                    const uint32_t n[4] = {(words[i] << 4) & 0x00F000F0u, words[i] & 0x00F000F0u,
-                                           (words[i] >> 4) & 0x00F000F0u, (words[i] >> 8) & 0x00F000F0u};
+                    for (int i = 0; i < 4; i++) {
+                        // nibbles (0,4), (1,5), (2,6), (3,7) of the word, each pair brought to bits 4..7 of its half:
+                        // the masked nibble is the fp16 subnormal q * 2^-20 and the scale carries the 2^20
+                        const uint32_t n[4] = {(words[i] << 4) & 0x00F000F0u, words[i] & 0x00F000F0u,
+                                               (words[i] >> 4) & 0x00F000F0u, (words[i] >> 8) & 0x00F000F0u};
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        __half2 wv;
-                        if (small) {
-                            // the masked nibble is the subnormal q * 2^-20; scale carries the 2^20
-                            wv = __hfma2(*reinterpret_cast<const __half2*>(&n[j]), sc, bi);
-                        } else {
-                            // large scale: (1024 + 16 q) / 16 - 64 = q exactly, then q * scale + bias
-                            const uint32_t h = n[j] | 0x64006400u;
-                            wv = __hfma2(__hfma2(*reinterpret_cast<const __half2*>(&h), kMul, kSub), sc, bi);
+                        for (int j = 0; j < 4; j++) {
+                            const __half2 wv = __hfma2(*reinterpret_cast<const __half2*>(&n[j]), sc, bi);
+                            v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
                         }
-                        v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t n[4] = {(words[i] << 4) & 0x00F000F0u, words[i] & 0x00F000F0u,
+                                               (words[i] >> 4) & 0x00F000F0u, (words[i] >> 8) & 0x00F000F0u};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            __half2 wv;
+                            if (small) {
+                                wv = __hfma2(*reinterpret_cast<const __half2*>(&n[j]), sc, bi);
+                            } else {
+                                // large scale: (1024 + 16 q) / 16 - 64 = q exactly, then q * scale + bias
+                                const uint32_t h = n[j] | 0x64006400u;
+                                wv = __hfma2(__hfma2(*reinterpret_cast<const __half2*>(&h), kMul, kSub), sc, bi);
+                            }
+                            v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
+                        }
                     }
                 }
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 1);
@@ -366,7 +389,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 2);
                 __syncwarp();                                   // the per-lane dequant branches end here
                 tc_fence_after();
-                tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 + (sa * 2 + half) * (BK / 2) + khalf * 16, v);
+                tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + a_col(sa, half, khalf), v);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 // one arrival per warp: hundreds of arrivals on one barrier word serialise in shared memory
@@ -381,7 +404,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         __syncwarp();                                           // lane 0 issued the MMAs alone
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");

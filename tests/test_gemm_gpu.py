@@ -116,3 +116,22 @@ def test_gemm_round_trip_property_at_full_size(mlxq, oracle):
     sub = oracle.qmatmul(lay.packed[rows], lay.scales_raw[rows], lay.biases_raw[rows], synth.BF16, x1[:128], K, 4, 64)
     assert oracle.max_rel_err(y1[:128][:, rows], sub) < 1e-3
     mlxq.streamStatus(None, 0)
+
+
+def test_gemm_repeats_bit_for_bit_at_full_size(mlxq):
+    # 14336 x 4096, M = 2048, twelve calls on the same inputs: the pipeline's hand-offs (TMA rings, tensor-memory A
+    # ring, deferred epilogue) leave no room for timing to change a single bit.  Tensor-memory stores issued after the
+    # lanes of a warp had polled a barrier one by one showed up here as a few rows of one tile differing.
+    O, K, T = 14336, 4096, 2048
+    lay = synth.make_layer(O, K, 4, 64, synth.BF16, seed=31, keep_codes=False)
+    layer = DevLayer(mlxq, lay.packed, lay.scales_raw, lay.biases_raw, synth.BF16, K)
+    _, xv = synth.make_activations(T, K, synth.BF16, seed=100)
+    x = torch.from_numpy(xv).to("cuda").to(torch.bfloat16)
+    ys = [torch.empty((T, O), dtype=torch.float32, device="cuda") for _ in range(2)]
+    layer.linear.encode(None, x, K, ys[0], O, T)
+    for call in range(12):
+        layer.linear.encode(None, x, K, ys[1], O, T)
+        torch.cuda.synchronize()
+        differing = int((ys[1].view(torch.int32) != ys[0].view(torch.int32)).sum())
+        assert differing == 0, f"call {call}: {differing} outputs differ from the first call's"
+    mlxq.streamStatus(None, 0)
