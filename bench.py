@@ -44,6 +44,12 @@ def alg_bytes(O, K, bits, gs, M, s_size=2, x_size=2, y_size=4):
     return O * K * bits // 8 + 2 * O * (K // gs) * s_size + M * K * x_size + M * O * y_size
 
 
+def workload_name(layers):
+    per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1)
+    return (f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1, fp16 x, fp32 y; "
+            f"{layers} distinct weight sets per step ({layers * per_launch / 1e6:.0f} MB > L2)")
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -161,7 +167,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1 (CPU, one layer per step)"},
+        "config": {"workload": workload_name(LAYERS), "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS,
+                   "group_size": GS, "batch": 1, "launches_per_step": 1,
+                   "sample": "each CPU step is one of the workload's weight sets (a step of the GPU arm is 16 of them)"},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -324,8 +332,7 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1, fp16 x, fp32 y; "
-                                   f"{LAYERS} distinct weight sets per step ({LAYERS * per_launch / 1e6:.0f} MB > L2)",
+            "config": {"workload": workload_name(LAYERS),
                        "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS, "group_size": GS, "batch": 1,
                        "launches_per_step": LAYERS, "l2": "inputs larger than L2",
                        "parallelism": (f"row-shard x{world} + " + ("peer-store gather fused into the kernel" if fused else

@@ -414,22 +414,33 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
 
         const uint8_t* f0 = half0 + frag_off + s_begin * (4 * LB);
         const uint8_t* f1 = half1 + frag_off + s_begin * (4 * LB);
-        for (int s = s_begin; s < ((MLXQ_ABLATE & 2) ? s_begin : s_end); s++, f0 += 4 * LB, f1 += 4 * LB) {
-            uint32_t w[2][NW];
-            if constexpr ((MLXQ_ABLATE & 32) != 0) {
-#pragma unroll
-                for (int i = 0; i < NW; i++) { w[0][i] = (s + i) * 0x01010101u + lane; w[1][i] = (s - i) * 0x01010101u + lane; }
-            } else if constexpr (LB == 16) {
-                const uint4 v0 = *reinterpret_cast<const uint4*>(f0), v1 = *reinterpret_cast<const uint4*>(f1);
+        // the lane's words of both rows for one step
+        auto load_words = [&](const uint8_t* p0, const uint8_t* p1, uint32_t (&w)[2][NW]) {
+            if constexpr (LB == 16) {
+                const uint4 v0 = *reinterpret_cast<const uint4*>(p0), v1 = *reinterpret_cast<const uint4*>(p1);
                 w[0][0] = v0.x; w[0][1] = v0.y; w[0][2] = v0.z; w[0][3] = v0.w;
                 w[1][0] = v1.x; w[1][1] = v1.y; w[1][2] = v1.z; w[1][3] = v1.w;
             } else {
 #pragma unroll
                 for (int i = 0; i < NW / 2; i++) {
-                    const uint2 v0 = *(reinterpret_cast<const uint2*>(f0) + i), v1 = *(reinterpret_cast<const uint2*>(f1) + i);
+                    const uint2 v0 = *(reinterpret_cast<const uint2*>(p0) + i), v1 = *(reinterpret_cast<const uint2*>(p1) + i);
                     w[0][2 * i] = v0.x; w[0][2 * i + 1] = v0.y;
                     w[1][2 * i] = v1.x; w[1][2 * i + 1] = v1.y;
                 }
+            }
+        };
+        // narrow codes: the next step's words are fetched while this step's MMAs run
+        constexpr bool PREFETCH = NW <= 4;
+        uint32_t wn[2][NW];
+        if (PREFETCH && s_begin < s_end) load_words(f0, f1, wn);
+        for (int s = s_begin; s < ((MLXQ_ABLATE & 2) ? s_begin : s_end); s++, f0 += 4 * LB, f1 += 4 * LB) {
+            uint32_t w[2][NW];
+            if constexpr (PREFETCH) {
+#pragma unroll
+                for (int i = 0; i < NW; i++) { w[0][i] = wn[0][i]; w[1][i] = wn[1][i]; }
+                if (s + 1 < s_end) load_words(f0 + 4 * LB, f1 + 4 * LB, wn);
+            } else {
+                load_words(f0, f1, w);
             }
             const int gblock = s >> spg_shift;
             const int cyc_s = gblock & cyc_mask;
