@@ -65,10 +65,12 @@ constexpr int X_STAGE = BN * BK * 2;    // 16384 bytes
 constexpr int W_SLAB = BM * 128;        // 32768 bytes: 256 rows x 128 bytes, 128-byte swizzle
 constexpr int NUM_THREADS = 20 * 32;
 constexpr int W_PRODUCER = 2;           // warp that streams the packed weight slabs
-#ifndef MLXQ_MMA_WARP
-#define MLXQ_MMA_WARP 1
-#endif
-constexpr int MMA_WARP = MLXQ_MMA_WARP;  // warp whose lane 0 issues the MMAs; it also owns the tensor-memory allocation
+// Two warps issue the MMAs, one per 128-row half of the tile (lane 0 of each).  A single thread needs ~110 cycles
+// per tcgen05.mma (operands travel through uniform registers) while an M128 N128 K16 MMA executes in 64: with one
+// issuer the tensor pipe was busy a third of the time.  The halves use separate accumulators and separate A
+// columns, so nothing orders the two issuers against each other; stage and accumulator barriers count both.
+constexpr int MMA_WARP = 1;             // issuer of half 0; it also owns the tensor-memory allocation
+constexpr int MMA_WARP2 = 3;            // issuer of half 1
 constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16;
 constexpr int TMEM_COLS = 512;
 constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
@@ -132,10 +134,10 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     const int total_tiles = a.m_tiles * a.n_tiles;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < S_X; i++) { mbar_init(&bars->full_x[i], 1); mbar_init(&bars->empty_x[i], 1); }
+        for (int i = 0; i < S_X; i++) { mbar_init(&bars->full_x[i], 1); mbar_init(&bars->empty_x[i], 2); }
         for (int i = 0; i < S_W; i++) { mbar_init(&bars->full_w[i], 1); mbar_init(&bars->empty_w[i], DEQ_WARPS); }
-        for (int i = 0; i < S_A; i++) { mbar_init(&bars->full_a[i], DEQ_WARPS); mbar_init(&bars->empty_a[i], 1); }
-        mbar_init(&bars->d_full, 1);
+        for (int i = 0; i < S_A; i++) { mbar_init(&bars->full_a[i], DEQ_WARPS); mbar_init(&bars->empty_a[i], 2); }
+        mbar_init(&bars->d_full, 2);
         mbar_init(&bars->d_empty, DEQ_WARPS);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -196,8 +198,8 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     if (global_ns() - t0 > WAIT_NS) break;
             }
         }
-    } else if (warp == MMA_WARP) {
-        // ---- MMA issuer ------------------------------------------------------------------------------------
+    } else if (warp == MMA_WARP || warp == MMA_WARP2) {
+        // ---- MMA issuers ------------------------------------------------------------------------------------
         if (lane == 0) {
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
@@ -209,10 +211,10 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     if (!mbar_wait(&bars->full_x[s], (it / S_X) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     if (!mbar_wait(&bars->full_a[sa], (it / S_A) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     tc_fence_after();
-                    if (tile_i == 0 && ks < 24) GTRACE(ks * 2);
+                    if (warp == MMA_WARP && tile_i == 0 && ks < 24) GTRACE(ks * 2);
                     const uint64_t bdesc = smem_desc_sw128(smem_u32(x_tiles + s * X_STAGE));
-#pragma unroll
-                    for (int half = 0; half < 2; half++) {
+                    {
+                        const int half = warp == MMA_WARP ? 0 : 1;
                         const uint32_t d_addr = tmem + D_COL0 + half * BN;
 #pragma unroll
                         for (int kk = 0; kk < BK / 16; kk++)
@@ -220,7 +222,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     }
                     tc_commit(&bars->empty_x[s]);      // the activation tile of stage s is free again
                     tc_commit(&bars->empty_a[sa]);     // so is the A stage in tensor memory
-                    if (tile_i == 0 && ks < 24) GTRACE(ks * 2 + 1);
+                    if (warp == MMA_WARP && tile_i == 0 && ks < 24) GTRACE(ks * 2 + 1);
                 }
                 if (ok) tc_commit(&bars->d_full);      // accumulators of this tile are complete
             }
@@ -277,6 +279,17 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             }
         };
         int pending_tile = -1;
+        // A stage's tensor-memory store is published to the MMA issuers (wait for the store, fence, one arrival per
+        // warp) only after the next stage's unpacking, so the store's latency is not waited out with idle hands.
+        int stored_sa = -1;
+        auto publish = [&]() {
+            if (stored_sa < 0) return;
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->full_a[stored_sa]);
+            stored_sa = -1;
+        };
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, tile_i++) {
             const int m_tile = tile % a.m_tiles;
             const int row0 = m_tile * BM + half * 128;
@@ -290,6 +303,9 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const bool packed4 = a.gs_shift == 6 && a.s_dtype != DT_F32 && (gpr & 3) == 0;
             uint32_t s_nxt[W_SPAN], b_nxt[W_SPAN], s_cur[W_SPAN], b_cur[W_SPAN];
             auto fetch_slab = [&](int ks0) {
+#ifdef MLXQ_GEMM_ABLATE
+                if (MLXQ_GEMM_ABLATE & 1) { s_nxt[0] = s_nxt[1] = 0x10101010u + ks0; b_nxt[0] = b_nxt[1] = 0x10101010u; return; }
+#endif
                 if (packed4) {
                     const unsigned short* sp = reinterpret_cast<const unsigned short*>(a.s) + srow + ks0;
                     const unsigned short* bp = reinterpret_cast<const unsigned short*>(a.b) + srow + ks0;
@@ -309,6 +325,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 if (ks == S_A && pending_tile >= 0) {
                     // The A ring now holds this tile's first stages; the MMAs wait for the previous tile's
                     // accumulators to be read, which is what this does.
+                    publish();
                     epilogue(pending_tile, tile_i - 1);
                     pending_tile = -1;
                 }
@@ -341,8 +358,13 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(209 + (wi - 1) * 2);
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4);
                 // row of 128 bytes, 16-byte chunk (sub*2 + khalf), stored with the 128-byte swizzle (chunk ^ row%8)
+                // (fetching the next stage's chunk a stage early was tried: slower, 660 vs 690 TFLOP/s)
                 const int wr = half * 128 + r;
+#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 4)
+                const uint4 pk = make_uint4(0x12345678u + it, 0x9abcdef0u, 0x0f1e2d3cu + lane, 0x4b5a6978u);
+#else
                 const uint4 pk = *reinterpret_cast<const uint4*>(w_slabs + sw * W_SLAB + wr * 128 + (((sub * 2 + khalf) ^ (wr & 7)) << 4));
+#endif
                 if (sub == W_SPAN - 1 || ks == k_stages - 1) {
                     // last read of the slab by this warp
                     __syncwarp();
@@ -385,18 +407,16 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     }
                 }
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 1);
+                publish();                                      // the previous stage's store has had this stage's arithmetic to land
                 if (it >= S_A && !mbar_wait_warp(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 2);
                 __syncwarp();                                   // the per-lane dequant branches end here
                 tc_fence_after();
                 tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + a_col(sa, half, khalf), v);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                // one arrival per warp: hundreds of arrivals on one barrier word serialise in shared memory
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->full_a[sa]);
+                stored_sa = sa;
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 3);
             }
+            publish();                                          // the tile's last stage
             if (ok) pending_tile = tile;
         }
         if (pending_tile >= 0) epilogue(pending_tile, tile_i - 1);
