@@ -119,12 +119,14 @@ MLXQ_API int mlxq_linear_forward(mlxq_linear_t h, mlxq_stream_t stream, const vo
 
 /* mlxq_linear_forward for callers that cannot allocate device memory.  It has no counterpart in the reference.
  * The tensor-core GEMM of mlxq_linear_forward stages an fp16 copy of the activations (T * in_dim * 2 bytes)
- * in pool memory it allocates on the stream.  A host that has given all free device memory to its own caches,
- * or that must not enter the CUDA allocator while it runs (an allocator lock held by the host, a latency
- * budget that cannot absorb the allocator's device synchronisation), calls this entry point instead: the
- * staged copy lives in a fixed 32 MiB array inside the library (MLXQ_STATIC_SCRATCH_BYTES), no cudaMalloc,
+ * and a table of the layer's scales and biases (out_dim * in_dim / 8 bytes) in pool memory it allocates on
+ * the stream.  A host that has given all free device memory to its own caches, or that must not enter the
+ * CUDA allocator while it runs (an allocator lock held by the host, a latency budget that cannot absorb the
+ * allocator's device synchronisation), calls this entry point instead: both live in a fixed array inside the
+ * library (32 MiB = MLXQ_STATIC_SCRATCH_BYTES for the activations, 16 MiB for the table), no cudaMalloc,
  * cudaFree or other allocating routine is called, and results are the same as mlxq_linear_forward's.
- *   - Batches with T * in_dim * 2 above the array's size are rejected with MLXQ_INVALID_ARGUMENT (split them).
+ *   - Batches with T * in_dim * 2 above 32 MiB, and layers with out_dim * in_dim / 8 above 16 MiB (rows
+ *     rounded up to 256), are rejected with MLXQ_INVALID_ARGUMENT (split the batch; shard the layer).
  *   - Batches the GEMM does not take (T <= 16, fp32 activations, other bit widths) run on kernels that use no
  *     scratch memory, exactly as in mlxq_linear_forward.
  *   - Every call on a device shares the one array, which keeps whatever the last call wrote: calls that

@@ -73,6 +73,7 @@ constexpr int MMA_WARP = 1;             // issuer of half 0; it also owns the te
 constexpr int MMA_WARP2 = 3;            // issuer of half 1
 constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16;
 constexpr int TMEM_COLS = 512;
+constexpr uint32_t SCALE_MARKER = 0x7E00u;   // fp16 NaN in a staged entry: scale * 2^20 does not fit fp16
 constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
 constexpr int A_COL0 = 2 * BN;          // A ring: S_A stages x 2 halves x 32 columns
 // First tensor-memory column of the 16 columns (32 fp16) that one dequantising warp stores for ring stage `sa`,
@@ -108,6 +109,8 @@ struct GemmArgs {
     int gs_shift;        // log2(gs): group sizes are powers of two here
     int m_tiles, n_tiles;
     uint32_t idesc;
+    const uint4* pairs;  // staged scales and biases, see stage_scales_kernel
+    int o_pad;           // rows of the staged table: m_tiles * BM
 };
 
 // Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128 bytes, 8-row
@@ -295,30 +298,19 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const int row0 = m_tile * BM + half * 128;
             const int row = min(row0 + r, a.O - 1);            // rows past the end read a valid row; never stored
             const size_t srow = static_cast<size_t>(row) * gpr;
-            // Scales and biases are fetched a whole weight slab (W_SPAN stages) ahead as raw bits -- a dependent
-            // global load (or a conversion of its result) per stage would put the load's full latency on every
-            // stage of every dequantising warp.  With 16-bit scales and one group per stage (group size 64) a
-            // slab's four scales are 8 contiguous bytes: one 64-bit load each for scales and biases.  The loads
-            // are volatile asm so that they are issued here and not re-materialised next to their use.
-            const bool packed4 = a.gs_shift == 6 && a.s_dtype != DT_F32 && (gpr & 3) == 0;
-            uint32_t s_nxt[W_SPAN], b_nxt[W_SPAN], s_cur[W_SPAN], b_cur[W_SPAN];
-            auto fetch_slab = [&](int ks0) {
+            // Scales and biases come from the table stage_scales_kernel wrote for this call: one 16-byte entry per
+            // (weight slab, K half, row) holding, for the slab's four stages, fp16(scale * 2^20) and fp16(bias).  A
+            // warp's 32 rows are 512 contiguous bytes, and the entry is fetched a whole slab ahead (volatile asm,
+            // so that the load is issued here and not re-materialised next to its use): the original tensors
+            // would cost every warp 32 separate sectors per load, and a conversion per stage.
+            const uint4* ptab = a.pairs + static_cast<size_t>(khalf) * a.o_pad + (m_tile * BM + half * 128 + r);
+            uint32_t p_nxt[4], p_cur[4] = {0u, 0u, 0u, 0u};
+            auto fetch_slab = [&](int slab) {
 #ifdef MLXQ_GEMM_ABLATE
-                if (MLXQ_GEMM_ABLATE & 1) { s_nxt[0] = s_nxt[1] = 0x10101010u + ks0; b_nxt[0] = b_nxt[1] = 0x10101010u; return; }
+                if (MLXQ_GEMM_ABLATE & 1) { p_nxt[0] = p_nxt[1] = p_nxt[2] = p_nxt[3] = 0x10103c00u + slab; return; }
 #endif
-                if (packed4) {
-                    const unsigned short* sp = reinterpret_cast<const unsigned short*>(a.s) + srow + ks0;
-                    const unsigned short* bp = reinterpret_cast<const unsigned short*>(a.b) + srow + ks0;
-                    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(s_nxt[0]), "=r"(s_nxt[1]) : "l"(sp));
-                    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(b_nxt[0]), "=r"(b_nxt[1]) : "l"(bp));
-                } else {
-#pragma unroll
-                    for (int j = 0; j < W_SPAN; j++) {
-                        const int grp = min(((ks0 + j) * BK + khalf * 32) >> a.gs_shift, gpr - 1);
-                        s_nxt[j] = load_scalar_raw(a.s, a.s_dtype, srow + grp);
-                        b_nxt[j] = load_scalar_raw(a.b, a.s_dtype, srow + grp);
-                    }
-                }
+                const uint4* e = ptab + static_cast<size_t>(slab) * 2 * a.o_pad;
+                asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(p_nxt[0]), "=r"(p_nxt[1]), "=r"(p_nxt[2]), "=r"(p_nxt[3]) : "l"(e));
             };
             fetch_slab(0);
             for (int ks = 0; ks < k_stages; ks++, it++) {
@@ -334,25 +326,26 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 if (sub == 0) {
                     wi++;                                       // same count as the producer: a new slab per W_SPAN stages of a tile
 #pragma unroll
-                    for (int j = 0; j < W_SPAN; j++) { s_cur[j] = s_nxt[j]; b_cur[j] = b_nxt[j]; }
-                    if (ks + W_SPAN < k_stages) fetch_slab(ks + W_SPAN);
+                    for (int j = 0; j < 4; j++) p_cur[j] = p_nxt[j];
+                    if (ks + W_SPAN < k_stages) fetch_slab(ks / W_SPAN + 1);
                 }
                 const int sw = (wi - 1) % S_W;
-                // scale and bias of the group these 32 codes belong to (groups are multiples of 32 codes)
-                uint32_t sraw, braw;
-                if (packed4) {
-                    const uint32_t sw2 = (sub & 2) ? s_cur[1] : s_cur[0], bw2 = (sub & 2) ? b_cur[1] : b_cur[0];
-                    sraw = (sub & 1) ? (sw2 >> 16) : (sw2 & 0xFFFFu);
-                    braw = (sub & 1) ? (bw2 >> 16) : (bw2 & 0xFFFFu);
-                } else {
-                    sraw = s_cur[0]; braw = b_cur[0];
+                // this stage's entry: low half fp16(scale * 2^20), or the marker when the scale is too large for
+                // that; high half fp16(bias)
+                uint32_t entry = p_cur[0];
 #pragma unroll
-                    for (int j = 1; j < W_SPAN; j++) if (sub == j) { sraw = s_cur[j]; braw = b_cur[j]; }
+                for (int j = 1; j < 4; j++) if (sub == j) entry = p_cur[j];
+                const bool small = (entry & 0xFFFFu) != SCALE_MARKER;
+                const uint32_t bi_bits = __byte_perm(entry, entry, 0x3232);
+                const __half2 bi = *reinterpret_cast<const __half2*>(&bi_bits);
+                uint32_t sc_bits = __byte_perm(entry, entry, 0x1010);
+                if (!small) {
+                    // rare: the scale itself (times one), from the layer's tensor
+                    const int grp = min((ks * BK + khalf * 32) >> a.gs_shift, gpr - 1);
+                    const __half2 s2 = __float2half2_rn(load_scalar(a.s, a.s_dtype, srow + grp));
+                    sc_bits = *reinterpret_cast<const uint32_t*>(&s2);
                 }
-                const float sf = scalar_from_raw(sraw, a.s_dtype);
-                const __half2 bi = __float2half2_rn(scalar_from_raw(braw, a.s_dtype));
-                const bool small = fabsf(sf) < 0.0624f;         // scale * 2^20 stays inside fp16
-                const __half2 sc = __float2half2_rn(small ? sf * 1048576.0f : sf);
+                const __half2 sc = *reinterpret_cast<const __half2*>(&sc_bits);
                 if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(208 + (wi - 1) * 2);
                 if (sub == 0 && !mbar_wait_warp(&bars->full_w[sw], ((wi - 1) / S_W) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                 if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(209 + (wi - 1) * 2);
@@ -458,6 +451,48 @@ __global__ void stage_x_kernel(const uint16_t* __restrict__ x, int is_bf16, long
     }
 }
 
+// Scales and biases -> the table the dequantising warps read: entry [(slab * 2 + khalf) * o_pad + row] holds, for the
+// four K stages of weight slab `slab`, (fp16(scale * 2^20) | fp16(bias) << 16) of the group that the 32 codes
+// (stage, khalf) of `row` belong to.  Scales of magnitude 0.0624 and above get SCALE_MARKER instead (the kernel
+// then takes the scale from the layer's tensor).  Rows past O and stages past K hold zeros.
+__global__ void stage_scales_kernel(const void* __restrict__ s, const void* __restrict__ b, int s_dtype, int O, int o_pad, int gpr,
+                                    int gs_shift, int k_stages, int n_slabs, uint4* __restrict__ out) {
+    const long long n = static_cast<long long>(n_slabs) * o_pad;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i % o_pad);
+        const int slab = static_cast<int>(i / o_pad);
+        uint32_t e[2][4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int ks = slab * W_SPAN + j;
+            uint32_t prev = 0u;
+            int prev_grp = -1;
+#pragma unroll
+            for (int khalf = 0; khalf < 2; khalf++) {
+                uint32_t v = 0u;
+                if (row < O && ks < k_stages) {
+                    const int grp = min((ks * BK + khalf * 32) >> gs_shift, gpr - 1);
+                    if (grp == prev_grp) {
+                        v = prev;                   // groups of 64 and more: both K halves of a stage share one
+                    } else {
+                        const float sf = load_scalar(s, s_dtype, static_cast<size_t>(row) * gpr + grp);
+                        const float bf = load_scalar(b, s_dtype, static_cast<size_t>(row) * gpr + grp);
+                        const __half hs = __float2half_rn(sf * 1048576.0f), hb = __float2half_rn(bf);
+                        const uint32_t lo = fabsf(sf) < 0.0624f ? static_cast<uint32_t>(__half_as_ushort(hs)) : SCALE_MARKER;
+                        v = lo | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
+                    }
+                    prev = v;
+                    prev_grp = grp;
+                }
+                e[khalf][j] = v;
+            }
+        }
+        out[static_cast<size_t>(slab) * 2 * o_pad + row] = make_uint4(e[0][0], e[0][1], e[0][2], e[0][3]);
+        out[(static_cast<size_t>(slab) * 2 + 1) * o_pad + row] = make_uint4(e[1][0], e[1][1], e[1][2], e[1][3]);
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -533,42 +568,36 @@ int qgemm_tile_tokens(const GemmLayer& L, int x_dtype, long long x_stride, const
     return BN;
 }
 
-cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why) {
-    *why = "";
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] {
-        attr_err = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    });
-    if (attr_err != cudaSuccess) { *why = "shared-memory opt-in"; return attr_err; }
-    // The activations are rewritten as fp16 in the staged order into stream-ordered scratch (see the header).
-    const void* x = c.x;
-    long long x_stride = c.x_stride;
-    __half* scratch = nullptr;
-    {
-        cudaMemPool_t pool = scratch_pool(L.device);
-        if (!pool) { *why = "scratch pool"; return cudaErrorMemoryAllocation; }
-        cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), static_cast<size_t>(c.T) * L.K * 2, pool, st);
-        if (e != cudaSuccess) { *why = "scratch allocation"; return e; }
-        const long long n = c.T * (L.K / 8);
-        const unsigned blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 8 ? n / 256 + 1 : 148LL * 8);
-        stage_x_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_dtype == DT_BF16 ? 1 : 0, c.x_stride, scratch, c.T, L.K);
-        x = scratch;
-        x_stride = L.K;
+namespace {
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+// Bytes of per-call scratch: the fp16 copy of the activations and the staged scale/bias table.
+size_t x_bytes(const GemmLayer& L, long long T) { return align256(static_cast<size_t>(T) * L.K * 2); }
+size_t table_bytes(const GemmLayer& L) {
+    const size_t n_slabs = (static_cast<size_t>(L.K) / BK + W_SPAN - 1) / W_SPAN;
+    const size_t o_pad = (static_cast<size_t>(L.O) + BM - 1) / BM * BM;
+    return n_slabs * 2 * o_pad * sizeof(uint4);
+}
+
+// Opts the kernel into its shared-memory size, once per device (function attributes belong to a device's context;
+// the caller has made `device` current).
+cudaError_t gemm_attr(int device) {
+    static std::mutex mu;
+    static bool done[64] = {};
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!done[device]) {
+        const cudaError_t e = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        done[device] = true;
     }
-    CUtensorMap map_w, map_x;
-    if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),
-                     static_cast<uint64_t>(L.K) / 2, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B)) {
-        if (scratch) cudaFreeAsync(scratch, st);
-        *why = "tensor map of the packed weights";
-        return cudaErrorInvalidValue;
-    }
-    if (!make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT16, x, static_cast<uint64_t>(L.K), static_cast<uint64_t>(c.T),
-                     static_cast<uint64_t>(x_stride) * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
-        if (scratch) cudaFreeAsync(scratch, st);
-        *why = "tensor map of the activations";
-        return cudaErrorInvalidValue;
-    }
+    return cudaSuccess;
+}
+
+// The two pre-passes (activations -> fp16 in the staged order, scales/biases -> the dequantisers' table) and the
+// GEMM, all on `st`; `xs` (x_bytes(L, T)) and `pairs` (table_bytes(L)) are their workspace, 256-byte aligned.
+cudaError_t enqueue_gemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st, __half* xs, uint4* pairs, const char** why) {
     GemmArgs a;
     a.s = L.s; a.b = L.b; a.bias = L.bias; a.y = c.y; a.err = c.err; a.y_stride = c.y_stride;
     a.s_dtype = L.s_dtype; a.bias_dtype = L.bias_dtype; a.y_dtype = c.y_dtype;
@@ -577,6 +606,28 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     while ((1 << a.gs_shift) < L.gs) a.gs_shift++;
     a.m_tiles = (L.O + BM - 1) / BM;
     a.n_tiles = static_cast<int>((c.T + BN - 1) / BN);
+    a.pairs = pairs;
+    a.o_pad = a.m_tiles * BM;
+    const int k_stages = L.K / BK, n_slabs = (k_stages + W_SPAN - 1) / W_SPAN;
+    {
+        const long long n = c.T * (L.K / 8);
+        const unsigned blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 8 ? n / 256 + 1 : 148LL * 8);
+        stage_x_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_dtype == DT_BF16 ? 1 : 0, c.x_stride, xs, c.T, L.K);
+        const long long ns = static_cast<long long>(n_slabs) * a.o_pad;
+        const unsigned sblocks = static_cast<unsigned>(ns / 256 + 1 < 148LL * 8 ? ns / 256 + 1 : 148LL * 8);
+        stage_scales_kernel<<<sblocks, 256, 0, st>>>(L.s, L.b, L.s_dtype, L.O, a.o_pad, L.K / L.gs, a.gs_shift, k_stages, n_slabs, pairs);
+    }
+    CUtensorMap map_w, map_x;
+    if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),
+                     static_cast<uint64_t>(L.K) / 2, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        *why = "tensor map of the packed weights";
+        return cudaErrorInvalidValue;
+    }
+    if (!make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT16, xs, static_cast<uint64_t>(L.K), static_cast<uint64_t>(c.T),
+                     static_cast<uint64_t>(L.K) * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        *why = "tensor map of the activations";
+        return cudaErrorInvalidValue;
+    }
     // instruction descriptor: fp32 accumulate (bit 4), A and B fp16 (format 0 at bits 7 and 10), both K-major,
     // N >> 3 at bit 17, M >> 4 at bit 24
     a.idesc = (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
@@ -584,81 +635,70 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     const int sms = sm_count(L.device);
     const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
     qgemm4_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
-    const cudaError_t launched = cudaGetLastError();
-    if (scratch) cudaFreeAsync(scratch, st);      // stream-ordered: released after the GEMM has read it
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why) {
+    *why = "";
+    if (const cudaError_t ae = gemm_attr(L.device)) { *why = "shared-memory opt-in"; return ae; }
+    // Workspace from the library's stream-ordered pool: allocated and released in stream order around the call.
+    cudaMemPool_t pool = scratch_pool(L.device);
+    if (!pool) { *why = "scratch pool"; return cudaErrorMemoryAllocation; }
+    uint8_t* scratch = nullptr;
+    cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), x_bytes(L, c.T) + table_bytes(L), pool, st);
+    if (e != cudaSuccess) { *why = "scratch allocation"; return e; }
+    const cudaError_t launched = enqueue_gemm(L, c, st, reinterpret_cast<__half*>(scratch),
+                                              reinterpret_cast<uint4*>(scratch + x_bytes(L, c.T)), why);
+    cudaFreeAsync(scratch, st);                   // stream-ordered: released after the GEMM has read it
     return launched;
 }
 
 // ---- the GEMM without any allocation -------------------------------------------------------------------------
 // Some hosts must not allocate device memory while they run: a serving loop that has handed every free byte
 // to its KV cache, a host whose allocator is locked during its hot loop, a caller inside a region where
-// cudaMalloc would synchronise the device.  For them the staged fp16 copy of the activations goes into this
-// fixed array instead of pool memory.  The array is part of the library image: every GPU that loads the
-// library holds its 32 MiB until the process exits.  Its contents are whatever the last call left; nothing in
-// it needs to start at zero (each call rewrites the [T, K] region it later reads).  All calls on a device share
-// it, so two calls that overlap on the GPU (different streams) race.
-constexpr size_t STATIC_SCRATCH_BYTES = 32u << 20;
-static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+// cudaMalloc would synchronise the device.  For them the call's workspace -- the staged fp16 copy of the
+// activations (up to 32 MiB) and the staged scale/bias table of the layer (up to 16 MiB) -- lives in this fixed
+// array instead of pool memory.  The array is part of the library image: every GPU that loads the library holds
+// its 48 MiB until the process exits.  Its contents are whatever the last call left; nothing in it needs to start
+// at zero (each call rewrites the regions it later reads).  All calls on a device share it, so two calls that
+// overlap on the GPU (different streams) race.
+constexpr size_t STATIC_X_BYTES = 32u << 20;
+constexpr size_t STATIC_TABLE_BYTES = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_X_BYTES + STATIC_TABLE_BYTES];
 
-size_t qgemm_static_capacity() { return STATIC_SCRATCH_BYTES; }
+size_t qgemm_static_capacity() { return STATIC_X_BYTES; }
 
 cudaError_t launch_qgemm_static(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why) {
     *why = "";
-    if (static_cast<unsigned long long>(c.T) * static_cast<unsigned long long>(L.K) * 2ull > STATIC_SCRATCH_BYTES) {
+    if (static_cast<unsigned long long>(c.T) * static_cast<unsigned long long>(L.K) * 2ull > STATIC_X_BYTES) {
         *why = "batch exceeds the static scratch";
+        return cudaErrorInvalidValue;
+    }
+    if (table_bytes(L) > STATIC_TABLE_BYTES) {
+        *why = "the layer's scale table exceeds the static scratch";
         return cudaErrorInvalidValue;
     }
     // In host code the array's name is only a handle: the device address comes from cudaGetSymbolAddress, asked
     // once per device with that device current (the caller has selected L.device).  This first call per device
     // also opts the kernel into its shared-memory size; make it before any stream capture.
     static std::mutex mu;
-    static __half* base[64] = {};
-    static bool attr_done[64] = {};
+    static unsigned char* base[64] = {};
     if (L.device < 0 || L.device >= 64) { *why = "device ordinal"; return cudaErrorInvalidDevice; }
-    __half* scratch = nullptr;
+    unsigned char* scratch = nullptr;
     {
         std::lock_guard<std::mutex> lk(mu);
         if (!base[L.device]) {
             void* p = nullptr;
             const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
             if (e != cudaSuccess) { *why = "address of the static scratch"; return e; }
-            base[L.device] = static_cast<__half*>(p);
-        }
-        if (!attr_done[L.device]) {
-            const cudaError_t e = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-            if (e != cudaSuccess) { *why = "shared-memory opt-in"; return e; }
-            attr_done[L.device] = true;
+            base[L.device] = static_cast<unsigned char*>(p);
         }
         scratch = base[L.device];
     }
-    const long long n = c.T * (L.K / 8);
-    const unsigned blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 8 ? n / 256 + 1 : 148LL * 8);
-    stage_x_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_dtype == DT_BF16 ? 1 : 0, c.x_stride, scratch, c.T, L.K);
-    CUtensorMap map_w, map_x;
-    if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),
-                     static_cast<uint64_t>(L.K) / 2, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B)) {
-        *why = "tensor map of the packed weights";
-        return cudaErrorInvalidValue;
-    }
-    if (!make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT16, scratch, static_cast<uint64_t>(L.K), static_cast<uint64_t>(c.T),
-                     static_cast<uint64_t>(L.K) * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
-        *why = "tensor map of the activations";
-        return cudaErrorInvalidValue;
-    }
-    GemmArgs a;
-    a.s = L.s; a.b = L.b; a.bias = L.bias; a.y = c.y; a.err = c.err; a.y_stride = c.y_stride;
-    a.s_dtype = L.s_dtype; a.bias_dtype = L.bias_dtype; a.y_dtype = c.y_dtype;
-    a.O = L.O; a.K = L.K; a.gs = L.gs; a.T = static_cast<int>(c.T);
-    a.gs_shift = 0;
-    while ((1 << a.gs_shift) < L.gs) a.gs_shift++;
-    a.m_tiles = (L.O + BM - 1) / BM;
-    a.n_tiles = static_cast<int>((c.T + BN - 1) / BN);
-    a.idesc = (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
-    const long long tiles = static_cast<long long>(a.m_tiles) * a.n_tiles;
-    const int sms = sm_count(L.device);
-    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-    qgemm4_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
-    return cudaGetLastError();
+    if (const cudaError_t ae = gemm_attr(L.device)) { *why = "shared-memory opt-in"; return ae; }
+    return enqueue_gemm(L, c, st, reinterpret_cast<__half*>(scratch), reinterpret_cast<uint4*>(scratch + STATIC_X_BYTES), why);
 }
 
 }  // namespace mlxq
