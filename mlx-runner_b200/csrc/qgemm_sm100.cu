@@ -90,7 +90,7 @@ struct Barriers {
     uint64_t full_a[S_A];
     uint64_t empty_a[S_A];
     uint64_t d_full;
-    uint64_t d_empty;
+    uint64_t d_empty[2];     // per 128-row half: its issuer restarts as soon as its eight epilogue warps have read
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -141,7 +141,8 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         for (int i = 0; i < S_W; i++) { mbar_init(&bars->full_w[i], 1); mbar_init(&bars->empty_w[i], DEQ_WARPS); }
         for (int i = 0; i < S_A; i++) { mbar_init(&bars->full_a[i], DEQ_WARPS); mbar_init(&bars->empty_a[i], 2); }
         mbar_init(&bars->d_full, 2);
-        mbar_init(&bars->d_empty, DEQ_WARPS);
+        mbar_init(&bars->d_empty[0], DEQ_WARPS / 2);
+        mbar_init(&bars->d_empty[1], DEQ_WARPS / 2);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -207,7 +208,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, tile_i++) {
-                if (tile_i > 0 && !mbar_wait(&bars->d_empty, (tile_i - 1) & 1, &bars->abort_flag, a.err)) break;
+                if (tile_i > 0 && !mbar_wait(&bars->d_empty[warp == MMA_WARP ? 0 : 1], (tile_i - 1) & 1, &bars->abort_flag, a.err)) break;
                 tc_fence_after();
                 for (int ks = 0; ks < k_stages; ks++, it++) {
                     const int s = it % S_X, sa = it % S_A;
@@ -260,7 +261,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     // last read of the accumulators by this warp: the MMA warp may start the next tile
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars->d_empty);
+                    if (lane == 0) mbar_arrive(&bars->d_empty[e_half]);
                 }
                 if (row < a.O) {
                     const int tok = tok0 + c * 32;
