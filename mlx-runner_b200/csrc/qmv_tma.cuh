@@ -429,8 +429,8 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                 }
             }
         };
-        // narrow codes: the next step's words are fetched while this step's MMAs run
-        constexpr bool PREFETCH = NW <= 4;
+        // (optionally the next step's words are fetched while this step's MMAs run)
+        constexpr bool PREFETCH = false;          // measured: fetching a step ahead costs 0.3 us per launch (11.7 vs 11.4)
         uint32_t wn[2][NW];
         if (PREFETCH && s_begin < s_end) load_words(f0, f1, wn);
         for (int s = s_begin; s < ((MLXQ_ABLATE & 2) ? s_begin : s_end); s++, f0 += 4 * LB, f1 += 4 * LB) {
