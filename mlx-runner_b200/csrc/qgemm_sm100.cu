@@ -73,6 +73,14 @@ constexpr int MMA_WARP = 1;             // issuer of half 0; it also owns the te
 constexpr int MMA_WARP2 = 3;            // issuer of half 1
 constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16;
 constexpr int TMEM_COLS = 512;
+// (timing aid, see MLXQ_GEMM_ABLATE)
+__host__ __device__ constexpr bool ablate_mma() {
+#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 16)
+    return true;
+#else
+    return false;
+#endif
+}
 constexpr uint32_t SCALE_MARKER = 0x7E00u;   // fp16 NaN in a staged entry: scale * 2^20 does not fit fp16
 constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
 constexpr int A_COL0 = 2 * BN;          // A ring: S_A stages x 2 halves x 32 columns
@@ -221,7 +229,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         const int half = warp == MMA_WARP ? 0 : 1;
                         const uint32_t d_addr = tmem + D_COL0 + half * BN;
 #pragma unroll
-                        for (int kk = 0; kk < BK / 16; kk++)
+                        for (int kk = 0; kk < (ablate_mma() ? 0 : BK / 16); kk++)
                             tc_mma_ts(d_addr, tmem + a_col(sa, half, kk >> 1) + (kk & 1) * 8, bdesc + static_cast<uint64_t>(kk * 2), a.idesc, (ks | kk) != 0);
                     }
                     tc_commit(&bars->empty_x[s]);      // the activation tile of stage s is free again
@@ -283,8 +291,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             }
         };
         int pending_tile = -1;
-        // A stage's tensor-memory store is published to the MMA issuers (wait for the store, fence, one arrival per
-        // warp) only after the next stage's unpacking, so the store's latency is not waited out with idle hands.
+        // A stage's tensor-memory store is published to the MMA issuers: wait for the store, fence, one arrival per warp.
         int stored_sa = -1;
         auto publish = [&]() {
             if (stored_sa < 0) return;
@@ -368,6 +375,12 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 uint32_t v[16];
                 // One decision per warp and stage, outside the unrolled loops: left per lane inside them, the
                 // compiler evaluated both dequant forms for every value (3x the half-precision FMAs).
+#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 2)
+                if (true) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v[i] = words[i & 3] + sc_bits + bi_bits;
+                } else
+#endif
                 if (__all_sync(0xffffffffu, small)) {
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
@@ -401,13 +414,18 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     }
                 }
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 1);
-                publish();                                      // the previous stage's store has had this stage's arithmetic to land
+#if !(defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 256))
                 if (it >= S_A && !mbar_wait_warp(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+#endif
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 2);
                 __syncwarp();                                   // the per-lane dequant branches end here
                 tc_fence_after();
+#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 8)
+                if (v[0] == 0x12345u && v[7] == 0x54321u)
+#endif
                 tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + a_col(sa, half, khalf), v);
                 stored_sa = sa;
+                publish();                                      // (publishing a stage late was tried: 1 % slower)
                 if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 3);
             }
             publish();                                          // the tile's last stage
