@@ -269,50 +269,8 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
     const int ctid = threadIdx.x;                                        // 0 .. 32 * TMA_CONSUMERS - 1
     constexpr int CTHREADS = TMA_CONSUMERS * 32;
 
-    // stage the activations once per CTA (see qmv_mma.cuh for the layout)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (q.peer.n > 0 && q.peer.wait_epoch != 0) {
-        // the activations may be the previous sharded call's gathered output: every peer must have finished it
-        if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], q.peer.wait_epoch, p.err);
-        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
-    }
-    {
-        const int cpr = K / 8;
-        for (int idx = ctid; idx < ((MLXQ_ABLATE & 4) ? 0 : q.T * cpr); idx += CTHREADS) {
-            const int tok = idx / cpr, k = (idx - tok * cpr) * 8;
-            float v[8];
-            if (q.x_dtype == DT_F16) XLoad<__half>::load8(reinterpret_cast<const __half*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
-            else if (q.x_dtype == DT_BF16) XLoad<__nv_bfloat16>::load8(reinterpret_cast<const __nv_bfloat16*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
-            else XLoad<float>::load8(reinterpret_cast<const float*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
-            float sum = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; i++) sum += v[i];
-            csum[idx] = sum;
-            if (p.split == 1) {
-                stage8<BITS>(xs + static_cast<size_t>(tok) * p.xstride, k, v);
-            } else {
-                float hi[8], lo[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) { hi[i] = __half2float(__float2half_rn(v[i])); lo[i] = v[i] - hi[i]; }
-                stage8<BITS>(xs + static_cast<size_t>(2 * tok) * p.xstride, k, hi);
-                stage8<BITS>(xs + static_cast<size_t>(2 * tok + 1) * p.xstride, k, lo);
-            }
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
-        const int cpg = 1 << (gs_shift - 3);
-        for (int idx = ctid; idx < p.xn * groups; idx += CTHREADS) {
-            const int xc = idx / groups, gi = idx - xc * groups;
-            float sum = 0.0f;
-            if (p.split == 1 || (xc & 1) == 0) {
-                const int tok = p.split == 1 ? xc : (xc >> 1);
-                for (int i = 0; i < cpg; i++) sum += csum[tok * cpr + gi * cpg + i];
-            }
-            xsum[idx] = sum;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
-    }
-
-    if (ctid == 0) TTRACE(16);
+    // Everything that does not depend on the activations comes first: under dependent launch it runs while the
+    // previous kernel of the stream is still finishing.
     // column bookkeeping, identical to qmv_mma_kernel
     const int run_grp_a = ((t * CL + mma_code_offset<BITS>(0)) >> gs_shift) & (G - 1);
     const int run_grp_b = ((t * CL + mma_code_offset<BITS>(NM / 2)) >> gs_shift) & (G - 1);
@@ -367,6 +325,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
     bool f_ok = false;
     int f_soff = 0;
     float2 f_xv = make_float2(0.0f, 0.0f);
+    int f_xoff = -1;
     bool lane_fast = NP == 1 && pair16 && n_drains == 1;
     {
         const int s = s_end - 1, gblock = s >> spg_shift, cyc_s = gblock & cyc_mask;
@@ -380,12 +339,57 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         f_ok = lane_fast && ok0;
         if (f_ok) {
             f_soff = tp.w_bytes + 2 * (g * groups + g0);
-            f_xv = *reinterpret_cast<const float2*>(xsum + c_xc[0][0] * groups + g0);
+            f_xoff = c_xc[0][0] * groups + g0;      // the sums themselves exist only after the staging below
         }
     }
     const bool fast_drain = __all_sync(0xffffffffu, lane_fast);
     f_ok = f_ok && fast_drain;
 
+    // stage the activations once per CTA (see qmv_mma.cuh for the layout)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (q.peer.n > 0 && q.peer.wait_epoch != 0) {
+        // the activations may be the previous sharded call's gathered output: every peer must have finished it
+        if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], q.peer.wait_epoch, p.err);
+        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
+    }
+    {
+        const int cpr = K / 8;
+        for (int idx = ctid; idx < ((MLXQ_ABLATE & 4) ? 0 : q.T * cpr); idx += CTHREADS) {
+            const int tok = idx / cpr, k = (idx - tok * cpr) * 8;
+            float v[8];
+            if (q.x_dtype == DT_F16) XLoad<__half>::load8(reinterpret_cast<const __half*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
+            else if (q.x_dtype == DT_BF16) XLoad<__nv_bfloat16>::load8(reinterpret_cast<const __nv_bfloat16*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
+            else XLoad<float>::load8(reinterpret_cast<const float*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) sum += v[i];
+            csum[idx] = sum;
+            if (p.split == 1) {
+                stage8<BITS>(xs + static_cast<size_t>(tok) * p.xstride, k, v);
+            } else {
+                float hi[8], lo[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) { hi[i] = __half2float(__float2half_rn(v[i])); lo[i] = v[i] - hi[i]; }
+                stage8<BITS>(xs + static_cast<size_t>(2 * tok) * p.xstride, k, hi);
+                stage8<BITS>(xs + static_cast<size_t>(2 * tok + 1) * p.xstride, k, lo);
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
+        const int cpg = 1 << (gs_shift - 3);
+        for (int idx = ctid; idx < p.xn * groups; idx += CTHREADS) {
+            const int xc = idx / groups, gi = idx - xc * groups;
+            float sum = 0.0f;
+            if (p.split == 1 || (xc & 1) == 0) {
+                const int tok = p.split == 1 ? xc : (xc >> 1);
+                for (int i = 0; i < cpg; i++) sum += csum[tok * cpr + gi * cpg + i];
+            }
+            xsum[idx] = sum;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
+    }
+
+    if (ctid == 0) TTRACE(16);
+    if (f_ok && f_xoff >= 0) f_xv = *reinterpret_cast<const float2*>(xsum + f_xoff);
     if (ctid == 0) TTRACE(17);
     // the CTA's blocks are dealt to the consumer groups in turn: group `stream` takes blocks stream, stream + n_streams, ...
     for (uint32_t bi = stream; blockIdx.x + static_cast<long long>(bi) * gridDim.x < tp.n_blocks; bi += n_streams) {
