@@ -352,35 +352,50 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], q.peer.wait_epoch, p.err);
         asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
     }
-    {
+    if (p.split == 1) {
+        // 16-bit activations: eight values per thread; the chunks of a group sit in consecutive lanes, so the
+        // per-group sums come from a few shuffles and one barrier suffices
+        const int cpr = K / 8, total = (MLXQ_ABLATE & 4) ? 0 : q.T * cpr;
+        const int cpg = 1 << (gs_shift - 3);
+        for (int base = 0; base < total; base += CTHREADS) {
+            const int idx = base + ctid;
+            const int tok = idx / cpr, k = (idx - tok * cpr) * 8;
+            float sum = 0.0f;
+            if (idx < total) {
+                float v[8];
+                if (q.x_dtype == DT_F16) XLoad<__half>::load8(reinterpret_cast<const __half*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
+                else XLoad<__nv_bfloat16>::load8(reinterpret_cast<const __nv_bfloat16*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
+#pragma unroll
+                for (int i = 0; i < 8; i++) sum += v[i];
+                stage8<BITS>(xs + static_cast<size_t>(tok) * p.xstride, k, v);
+            }
+            for (int o = 1; o < cpg; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (idx < total && (idx & (cpg - 1)) == 0) xsum[tok * groups + (k >> gs_shift)] = sum;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
+    } else {
         const int cpr = K / 8;
         for (int idx = ctid; idx < ((MLXQ_ABLATE & 4) ? 0 : q.T * cpr); idx += CTHREADS) {
             const int tok = idx / cpr, k = (idx - tok * cpr) * 8;
             float v[8];
-            if (q.x_dtype == DT_F16) XLoad<__half>::load8(reinterpret_cast<const __half*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
-            else if (q.x_dtype == DT_BF16) XLoad<__nv_bfloat16>::load8(reinterpret_cast<const __nv_bfloat16*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
-            else XLoad<float>::load8(reinterpret_cast<const float*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
+            XLoad<float>::load8(reinterpret_cast<const float*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k, v);
             float sum = 0.0f;
 #pragma unroll
             for (int i = 0; i < 8; i++) sum += v[i];
             csum[idx] = sum;
-            if (p.split == 1) {
-                stage8<BITS>(xs + static_cast<size_t>(tok) * p.xstride, k, v);
-            } else {
-                float hi[8], lo[8];
+            float hi[8], lo[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) { hi[i] = __half2float(__float2half_rn(v[i])); lo[i] = v[i] - hi[i]; }
-                stage8<BITS>(xs + static_cast<size_t>(2 * tok) * p.xstride, k, hi);
-                stage8<BITS>(xs + static_cast<size_t>(2 * tok + 1) * p.xstride, k, lo);
-            }
+            for (int i = 0; i < 8; i++) { hi[i] = __half2float(__float2half_rn(v[i])); lo[i] = v[i] - hi[i]; }
+            stage8<BITS>(xs + static_cast<size_t>(2 * tok) * p.xstride, k, hi);
+            stage8<BITS>(xs + static_cast<size_t>(2 * tok + 1) * p.xstride, k, lo);
         }
         asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory");
         const int cpg = 1 << (gs_shift - 3);
         for (int idx = ctid; idx < p.xn * groups; idx += CTHREADS) {
             const int xc = idx / groups, gi = idx - xc * groups;
             float sum = 0.0f;
-            if (p.split == 1 || (xc & 1) == 0) {
-                const int tok = p.split == 1 ? xc : (xc >> 1);
+            if ((xc & 1) == 0) {
+                const int tok = xc >> 1;
                 for (int i = 0; i < cpg; i++) sum += csum[tok * cpr + gi * cpg + i];
             }
             xsum[idx] = sum;
