@@ -36,6 +36,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "mlxq_device.cuh"
@@ -444,6 +445,299 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 }
 
 
+// ---- the wide tile: 128 weight rows x 256 tokens -----------------------------------------------------------------
+// Same pipeline, other tile.  Every dequantised weight now meets 256 tokens instead of 128, so the dequantisers
+// (the limiter of the 256 x 128 tile) do half the work per flop: a K stage is 128 rows x 64 codes, stored by
+// eight warps, and the sixteen dequantising warps take alternate stages.  Only one A block per stage lives in
+// tensor memory, so the A ring holds eight stages where the tall tile has four.  The accumulator is one
+// 128 x 256 fp32 block; two threads issue the MMAs, one per 128-token half (N = 128 each, separate columns,
+// separate halves of the activation tile).  Costs: 36 KB of operands per stage instead of 24 KB (L2 traffic),
+// and batches are padded to 256 tokens, so the tall tile stays in use for short batches.
+namespace wide {
+
+constexpr int BM = 128, BN = 256;
+constexpr int S_X = 4;                  // activation stages of 32 KB
+constexpr int S_W = 3;                  // weight slabs of 16 KB (128 rows x 128 bytes = W_SPAN stages)
+constexpr int S_A = 8;                  // TMEM stages of the A operand, 32 columns each
+constexpr int X_STAGE = BN * BK * 2;    // 32768
+constexpr int W_SLAB = BM * 128;        // 16384
+constexpr int D_COL0 = 0, A_COL0 = 256;
+constexpr int STAGE_WARPS = DEQ_WARPS / 2;   // warps that store one stage
+
+__host__ __device__ constexpr uint32_t a_col(int sa, int khalf) { return A_COL0 + static_cast<uint32_t>(sa * 32 + khalf * 16); }
+
+struct Barriers {
+    uint64_t full_x[S_X];
+    uint64_t empty_x[S_X];
+    uint64_t full_w[S_W];
+    uint64_t empty_w[S_W];
+    uint64_t full_a[S_A];
+    uint64_t empty_a[S_A];
+    uint64_t d_full;
+    uint64_t d_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr int SMEM_BYTES = S_X * X_STAGE + S_W * W_SLAB + sizeof(Barriers) + 1024;
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+qgemm4w_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* x_tiles = smem;
+    uint8_t* w_slabs = smem + S_X * X_STAGE;
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + S_X * X_STAGE + S_W * W_SLAB);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_stages = a.K / BK;
+    const int total_tiles = a.m_tiles * a.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S_X; i++) { mbar_init(&bars->full_x[i], 1); mbar_init(&bars->empty_x[i], 2); }
+        for (int i = 0; i < S_W; i++) { mbar_init(&bars->full_w[i], 1); mbar_init(&bars->empty_w[i], DEQ_WARPS); }
+        for (int i = 0; i < S_A; i++) { mbar_init(&bars->full_a[i], STAGE_WARPS); mbar_init(&bars->empty_a[i], 2); }
+        mbar_init(&bars->d_full, 2);
+        mbar_init(&bars->d_empty[0], DEQ_WARPS / 2);
+        mbar_init(&bars->d_empty[1], DEQ_WARPS / 2);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp == 0) {
+        // ---- TMA producer of the activations: one 256-token x 64 box per stage --------------------------------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int tok0 = (tile / a.m_tiles) * BN;
+                for (int ks = 0; ks < k_stages; ks++, it++) {
+                    const int s = it % S_X;
+                    if (it >= S_X && !mbar_wait(&bars->empty_x[s], ((it / S_X) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    mbar_expect_tx(&bars->full_x[s], X_STAGE);
+                    tma_load_2d(x_tiles + s * X_STAGE, &map_x, &bars->full_x[s], ks * BK, tok0);
+                }
+            }
+            for (uint32_t j = it > S_X ? it - S_X : 0; j < it; j++) {
+                const uint64_t t0 = global_ns();
+                while (!mbar_try_wait(&bars->full_x[j % S_X], (j / S_X) & 1))
+                    if (global_ns() - t0 > WAIT_NS) break;
+            }
+        }
+    } else if (warp == W_PRODUCER) {
+        // ---- TMA producer of packed weights: one slab (128 rows x 128 bytes = W_SPAN stages of K) per copy --------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+            uint32_t wi = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int row0 = (tile % a.m_tiles) * BM;
+                for (int ks = 0; ks < k_stages; ks += W_SPAN, wi++) {
+                    const int sw = wi % S_W;
+                    if (wi >= S_W && !mbar_wait(&bars->empty_w[sw], ((wi / S_W) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    mbar_expect_tx(&bars->full_w[sw], W_SLAB);
+                    tma_load_2d(w_slabs + sw * W_SLAB, &map_w, &bars->full_w[sw], ks * (BK / 2), row0);
+                }
+            }
+            for (uint32_t j = wi > S_W ? wi - S_W : 0; j < wi; j++) {
+                const uint64_t t0 = global_ns();
+                while (!mbar_try_wait(&bars->full_w[j % S_W], (j / S_W) & 1))
+                    if (global_ns() - t0 > WAIT_NS) break;
+            }
+        }
+    } else if (warp == MMA_WARP || warp == MMA_WARP2) {
+        // ---- MMA issuers: one per 128-token half of the tile ------------------------------------------------------------
+        if (lane == 0) {
+            const int nh = warp == MMA_WARP ? 0 : 1;
+            const uint32_t d_addr = tmem + D_COL0 + nh * 128;
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, tile_i++) {
+                if (tile_i > 0 && !mbar_wait(&bars->d_empty[nh], (tile_i - 1) & 1, &bars->abort_flag, a.err)) break;
+                tc_fence_after();
+                for (int ks = 0; ks < k_stages; ks++, it++) {
+                    const int s = it % S_X, sa = it % S_A;
+                    if (!mbar_wait(&bars->full_x[s], (it / S_X) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    if (!mbar_wait(&bars->full_a[sa], (it / S_A) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    tc_fence_after();
+                    // this half's 128 tokens are the second 16 KB of the stage (rows of 128 bytes, same swizzle phase)
+                    const uint64_t bdesc = smem_desc_sw128(smem_u32(x_tiles + s * X_STAGE + nh * (128 * 128)));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; kk++)
+                        tc_mma_ts(d_addr, tmem + a_col(sa, kk >> 1) + (kk & 1) * 8, bdesc + static_cast<uint64_t>(kk * 2), a.idesc, (ks | kk) != 0);
+                    tc_commit(&bars->empty_x[s]);
+                    tc_commit(&bars->empty_a[sa]);
+                }
+                if (ok) tc_commit(&bars->d_full);
+            }
+        }
+    } else if (warp >= DEQ_WARP0) {
+        // ---- dequantisers: one thread per (weight row, half of the 64-wide K slice), alternate stages ---------------------
+        const int dw = warp - DEQ_WARP0;
+        const int quad = warp & 3;                              // TMEM lane quadrant this warp may touch
+        const int khalf = (dw >> 2) & 1;                        // which 32 codes of the slice
+        const int par = dw >> 3;                                // the stages (by parity of the tile's stage index) this warp stores
+        const int r = quad * 32 + lane;                         // row within the tile
+        const int gpr = a.K >> a.gs_shift;
+        const __half2 kMul = __halves2half2(__float2half(0.0625f), __float2half(0.0625f));
+        const __half2 kSub = __halves2half2(__float2half(-64.0f), __float2half(-64.0f));
+        uint32_t it = 0, wi = 0, tile_i = 0;
+        bool ok = true;
+        // Epilogue: this warp drains its lane quadrant for 64 of the 256 token columns.
+        const int e_cols = (dw >> 2) * 64, e_nh = dw >> 3;
+        auto epilogue = [&](int tile, uint32_t index) {
+            const int row = (tile % a.m_tiles) * BM + r;
+            const int tok0 = (tile / a.m_tiles) * BN + e_cols;
+            if (!mbar_wait_warp(&bars->d_full, index & 1, &bars->abort_flag, a.err)) return;
+            tc_fence_after();
+            const float rb = (a.bias != nullptr && row < a.O) ? load_scalar(a.bias, a.bias_dtype, row) : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < 2; c++) {
+                uint32_t v[32];
+                __syncwarp();
+                tc_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + D_COL0 + e_cols + c * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (c == 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->d_empty[e_nh]);
+                }
+                if (row < a.O) {
+                    const int tok = tok0 + c * 32;
+                    const int nt = min(32, a.T - tok);
+                    if (a.y_dtype == DT_BF16) {
+                        __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(a.y) + static_cast<size_t>(tok) * a.y_stride + row;
+#pragma unroll
+                        for (int j = 0; j < 32; j++, yp += a.y_stride) if (j < nt) *yp = __float2bfloat16_rn(__uint_as_float(v[j]) + rb);
+                    } else if (a.y_dtype == DT_F16) {
+                        __half* yp = reinterpret_cast<__half*>(a.y) + static_cast<size_t>(tok) * a.y_stride + row;
+#pragma unroll
+                        for (int j = 0; j < 32; j++, yp += a.y_stride) if (j < nt) *yp = __float2half_rn(__uint_as_float(v[j]) + rb);
+                    } else {
+                        float* yp = reinterpret_cast<float*>(a.y) + static_cast<size_t>(tok) * a.y_stride + row;
+#pragma unroll
+                        for (int j = 0; j < 32; j++, yp += a.y_stride) if (j < nt) *yp = __uint_as_float(v[j]) + rb;
+                    }
+                }
+            }
+        };
+        int pending_tile = -1;
+        // the accumulators of the previous tile are drained once this tile's A ring is full (short K: at once)
+        const int epi_at = k_stages > S_A ? S_A : 0;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, tile_i++) {
+            const int m_tile = tile % a.m_tiles;
+            const int row = min(m_tile * BM + r, a.O - 1);
+            const size_t srow = static_cast<size_t>(row) * gpr;
+            const uint4* ptab = a.pairs + static_cast<size_t>(khalf) * a.o_pad + (m_tile * BM + r);
+            uint32_t p_nxt[4], p_cur[4] = {0u, 0u, 0u, 0u};
+            auto fetch_slab = [&](int slab) {
+                const uint4* e = ptab + static_cast<size_t>(slab) * 2 * a.o_pad;
+                asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(p_nxt[0]), "=r"(p_nxt[1]), "=r"(p_nxt[2]), "=r"(p_nxt[3]) : "l"(e));
+            };
+            fetch_slab(0);
+            for (int ks = 0; ks < k_stages; ks++, it++) {
+                if (ks == epi_at && pending_tile >= 0) {
+                    epilogue(pending_tile, tile_i - 1);
+                    pending_tile = -1;
+                }
+                const int sa = it % S_A;
+                const int sub = ks % W_SPAN;
+                const bool last_of_slab = sub == W_SPAN - 1 || ks == k_stages - 1;
+                if (sub == 0) {
+                    wi++;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) p_cur[j] = p_nxt[j];
+                    if (ks + W_SPAN < k_stages) fetch_slab(ks / W_SPAN + 1);
+                    if (!mbar_wait_warp(&bars->full_w[(wi - 1) % S_W], ((wi - 1) / S_W) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                }
+                const int sw = (wi - 1) % S_W;
+                if ((ks & 1) == par) {
+                    uint32_t entry = p_cur[0];
+#pragma unroll
+                    for (int j = 1; j < 4; j++) if (sub == j) entry = p_cur[j];
+                    const bool small = (entry & 0xFFFFu) != SCALE_MARKER;
+                    const uint32_t bi_bits = __byte_perm(entry, entry, 0x3232);
+                    const __half2 bi = *reinterpret_cast<const __half2*>(&bi_bits);
+                    uint32_t sc_bits = __byte_perm(entry, entry, 0x1010);
+                    if (!small) {
+                        const int grp = min((ks * BK + khalf * 32) >> a.gs_shift, gpr - 1);
+                        const __half2 s2 = __float2half2_rn(load_scalar(a.s, a.s_dtype, srow + grp));
+                        sc_bits = *reinterpret_cast<const uint32_t*>(&s2);
+                    }
+                    const __half2 sc = *reinterpret_cast<const __half2*>(&sc_bits);
+                    const uint4 pk = *reinterpret_cast<const uint4*>(w_slabs + sw * W_SLAB + r * 128 + (((sub * 2 + khalf) ^ (r & 7)) << 4));
+                    const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+                    uint32_t v[16];
+                    if (__all_sync(0xffffffffu, small)) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint32_t n[4] = {(words[i] << 4) & 0x00F000F0u, words[i] & 0x00F000F0u,
+                                                   (words[i] >> 4) & 0x00F000F0u, (words[i] >> 8) & 0x00F000F0u};
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const __half2 wv = __hfma2(*reinterpret_cast<const __half2*>(&n[j]), sc, bi);
+                                v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint32_t n[4] = {(words[i] << 4) & 0x00F000F0u, words[i] & 0x00F000F0u,
+                                                   (words[i] >> 4) & 0x00F000F0u, (words[i] >> 8) & 0x00F000F0u};
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                __half2 wv;
+                                if (small) {
+                                    wv = __hfma2(*reinterpret_cast<const __half2*>(&n[j]), sc, bi);
+                                } else {
+                                    const uint32_t h = n[j] | 0x64006400u;
+                                    wv = __hfma2(__hfma2(*reinterpret_cast<const __half2*>(&h), kMul, kSub), sc, bi);
+                                }
+                                v[i * 4 + j] = *reinterpret_cast<const uint32_t*>(&wv);
+                            }
+                        }
+                    }
+                    if (it >= S_A && !mbar_wait_warp(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
+                    __syncwarp();
+                    tc_fence_after();
+                    tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + a_col(sa, khalf), v);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->full_a[sa]);
+                }
+                if (last_of_slab) {
+                    // every chunk of the slab that this warp needs has been read
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+                }
+            }
+            if (ok) pending_tile = tile;
+        }
+        if (pending_tile >= 0) epilogue(pending_tile, tile_i - 1);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace wide
+
 // Activations -> fp16 in the staged order (0,4,1,5,2,6,3,7 inside every eight), eight elements per thread.
 // bf16 values beyond the fp16 range are clamped to +-65504.
 __global__ void stage_x_kernel(const uint16_t* __restrict__ x, int is_bf16, long long x_stride, __half* __restrict__ out, long long T, int K) {
@@ -578,13 +872,19 @@ cudaMemPool_t scratch_pool(int device) {
 
 }  // namespace
 
+// Batches of more than 128 tokens take the wide tile (128 rows x 256 tokens), shorter ones the tall one (256 x 128).
+static bool use_wide(long long T) {
+    static const int forced = [] { const char* e = std::getenv("MLXQ_GEMM_TILE"); return e ? (e[0] == 'w' ? 1 : e[0] == 't' ? 2 : 0) : 0; }();
+    return forced == 1 || (forced == 0 && T > 128);
+}
+
 int qgemm_tile_tokens(const GemmLayer& L, int x_dtype, long long x_stride, const void* x, long long T) {
     if (L.bits != 4 || L.K % BK != 0 || L.K < 2 * S_A * BK || L.gs < 32 || (L.gs & (L.gs - 1)) != 0 || L.O < 1 || T < 1) return 0;
     if (x_dtype != DT_F16 && x_dtype != DT_BF16) return 0;
     if ((reinterpret_cast<uintptr_t>(L.w) & 15u) != 0) return 0;
     if (x != nullptr && ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (x_stride * 2) % 16 != 0)) return 0;
     if (T > 0x7FFFFFFFLL) return 0;
-    return BN;
+    return use_wide(T) ? wide::BN : BN;
 }
 
 namespace {
@@ -607,7 +907,9 @@ cudaError_t gemm_attr(int device) {
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> lk(mu);
     if (!done[device]) {
-        const cudaError_t e = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(qgemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(wide::qgemm4w_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         done[device] = true;
     }
@@ -623,10 +925,12 @@ cudaError_t enqueue_gemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     a.O = L.O; a.K = L.K; a.gs = L.gs; a.T = static_cast<int>(c.T);
     a.gs_shift = 0;
     while ((1 << a.gs_shift) < L.gs) a.gs_shift++;
-    a.m_tiles = (L.O + BM - 1) / BM;
-    a.n_tiles = static_cast<int>((c.T + BN - 1) / BN);
+    const bool wide_tile = use_wide(c.T);
+    const int bm = wide_tile ? wide::BM : BM, bn = wide_tile ? wide::BN : BN;
+    a.m_tiles = (L.O + bm - 1) / bm;
+    a.n_tiles = static_cast<int>((c.T + bn - 1) / bn);
     a.pairs = pairs;
-    a.o_pad = a.m_tiles * BM;
+    a.o_pad = (L.O + BM - 1) / BM * BM;          // the table is padded to the tall tile's 256 rows for both
     const int k_stages = L.K / BK, n_slabs = (k_stages + W_SPAN - 1) / W_SPAN;
     {
         const long long n = c.T * (L.K / 8);
@@ -638,22 +942,23 @@ cudaError_t enqueue_gemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     }
     CUtensorMap map_w, map_x;
     if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),
-                     static_cast<uint64_t>(L.K) / 2, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                     static_cast<uint64_t>(L.K) / 2, 128, bm, CU_TENSOR_MAP_SWIZZLE_128B)) {
         *why = "tensor map of the packed weights";
         return cudaErrorInvalidValue;
     }
     if (!make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT16, xs, static_cast<uint64_t>(L.K), static_cast<uint64_t>(c.T),
-                     static_cast<uint64_t>(L.K) * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                     static_cast<uint64_t>(L.K) * 2, BK, bn, CU_TENSOR_MAP_SWIZZLE_128B)) {
         *why = "tensor map of the activations";
         return cudaErrorInvalidValue;
     }
     // instruction descriptor: fp32 accumulate (bit 4), A and B fp16 (format 0 at bits 7 and 10), both K-major,
     // N >> 3 at bit 17, M >> 4 at bit 24
-    a.idesc = (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+    a.idesc = (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
     const long long tiles = static_cast<long long>(a.m_tiles) * a.n_tiles;
     const int sms = sm_count(L.device);
     const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-    qgemm4_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
+    if (wide_tile) wide::qgemm4w_kernel<<<grid, NUM_THREADS, wide::SMEM_BYTES, st>>>(map_w, map_x, a);
+    else qgemm4_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
     return cudaGetLastError();
 }
 
