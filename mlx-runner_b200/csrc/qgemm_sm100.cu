@@ -456,7 +456,10 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 namespace wide {
 
 constexpr int BM = 128, BN = 256;
-constexpr int S_X = 4;                  // activation stages of 32 KB
+#ifndef MLXQ_WIDE_SX
+#define MLXQ_WIDE_SX 4
+#endif
+constexpr int S_X = MLXQ_WIDE_SX;       // activation stages of 32 KB
 constexpr int S_W = 3;                  // weight slabs of 16 KB (128 rows x 128 bytes = W_SPAN stages)
 constexpr int S_A = 8;                  // TMEM stages of the A operand, 32 columns each
 constexpr int X_STAGE = BN * BK * 2;    // 32768
@@ -740,11 +743,12 @@ qgemm4w_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // Activations -> fp16 in the staged order (0,4,1,5,2,6,3,7 inside every eight), eight elements per thread.
 // bf16 values beyond the fp16 range are clamped to +-65504.
-__global__ void stage_x_kernel(const uint16_t* __restrict__ x, int is_bf16, long long x_stride, __half* __restrict__ out, long long T, int K) {
+__device__ __forceinline__ void stage_x_part(const uint16_t* __restrict__ x, int is_bf16, long long x_stride, __half* __restrict__ out, long long T, int K,
+                                             unsigned block, unsigned blocks) {
     const long long chunks = static_cast<long long>(K) / 8;
     const long long n = T * chunks;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    for (long long i = block * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(blocks) * blockDim.x) {
         const long long t = i / chunks, c = i - t * chunks;
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + t * x_stride + c * 8));
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -768,11 +772,11 @@ __global__ void stage_x_kernel(const uint16_t* __restrict__ x, int is_bf16, long
 // four K stages of weight slab `slab`, (fp16(scale * 2^20) | fp16(bias) << 16) of the group that the 32 codes
 // (stage, khalf) of `row` belong to.  Scales of magnitude 0.0624 and above get SCALE_MARKER instead (the kernel
 // then takes the scale from the layer's tensor).  Rows past O and stages past K hold zeros.
-__global__ void stage_scales_kernel(const void* __restrict__ s, const void* __restrict__ b, int s_dtype, int O, int o_pad, int gpr,
-                                    int gs_shift, int k_stages, int n_slabs, uint4* __restrict__ out) {
+__device__ __forceinline__ void stage_scales_part(const void* __restrict__ s, const void* __restrict__ b, int s_dtype, int O, int o_pad, int gpr,
+                                                  int gs_shift, int k_stages, int n_slabs, uint4* __restrict__ out, unsigned block, unsigned blocks) {
     const long long n = static_cast<long long>(n_slabs) * o_pad;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    for (long long i = block * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(blocks) * blockDim.x) {
         const int row = static_cast<int>(i % o_pad);
         const int slab = static_cast<int>(i / o_pad);
         uint32_t e[2][4];
@@ -804,6 +808,18 @@ __global__ void stage_scales_kernel(const void* __restrict__ s, const void* __re
         out[static_cast<size_t>(slab) * 2 * o_pad + row] = make_uint4(e[0][0], e[0][1], e[0][2], e[0][3]);
         out[(static_cast<size_t>(slab) * 2 + 1) * o_pad + row] = make_uint4(e[1][0], e[1][1], e[1][2], e[1][3]);
     }
+}
+
+// Both pre-passes in one launch: the first `x_blocks` blocks rewrite the activations, the rest build the table.
+struct StageArgs {
+    const uint16_t* x; int is_bf16; long long x_stride; __half* xs; long long T; int K;
+    const void* s; const void* b; int s_dtype; int O; int o_pad; int gpr; int gs_shift; int k_stages; int n_slabs; uint4* pairs;
+    unsigned x_blocks;
+};
+__global__ void stage_inputs_kernel(const StageArgs g) {
+    if (blockIdx.x < g.x_blocks) stage_x_part(g.x, g.is_bf16, g.x_stride, g.xs, g.T, g.K, blockIdx.x, g.x_blocks);
+    else stage_scales_part(g.s, g.b, g.s_dtype, g.O, g.o_pad, g.gpr, g.gs_shift, g.k_stages, g.n_slabs, g.pairs,
+                           blockIdx.x - g.x_blocks, gridDim.x - g.x_blocks);
 }
 
 // ---- host side --------------------------------------------------------------------------------------------
@@ -934,11 +950,14 @@ cudaError_t enqueue_gemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     const int k_stages = L.K / BK, n_slabs = (k_stages + W_SPAN - 1) / W_SPAN;
     {
         const long long n = c.T * (L.K / 8);
-        const unsigned blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 8 ? n / 256 + 1 : 148LL * 8);
-        stage_x_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(c.x), c.x_dtype == DT_BF16 ? 1 : 0, c.x_stride, xs, c.T, L.K);
         const long long ns = static_cast<long long>(n_slabs) * a.o_pad;
-        const unsigned sblocks = static_cast<unsigned>(ns / 256 + 1 < 148LL * 8 ? ns / 256 + 1 : 148LL * 8);
-        stage_scales_kernel<<<sblocks, 256, 0, st>>>(L.s, L.b, L.s_dtype, L.O, a.o_pad, L.K / L.gs, a.gs_shift, k_stages, n_slabs, pairs);
+        StageArgs g;
+        g.x = static_cast<const uint16_t*>(c.x); g.is_bf16 = c.x_dtype == DT_BF16 ? 1 : 0; g.x_stride = c.x_stride; g.xs = xs; g.T = c.T; g.K = L.K;
+        g.s = L.s; g.b = L.b; g.s_dtype = L.s_dtype; g.O = L.O; g.o_pad = a.o_pad; g.gpr = L.K / L.gs; g.gs_shift = a.gs_shift;
+        g.k_stages = k_stages; g.n_slabs = n_slabs; g.pairs = pairs;
+        g.x_blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 6 ? n / 256 + 1 : 148LL * 6);
+        const unsigned s_blocks = static_cast<unsigned>(ns / 256 + 1 < 148LL * 4 ? ns / 256 + 1 : 148LL * 4);
+        stage_inputs_kernel<<<g.x_blocks + s_blocks, 256, 0, st>>>(g);
     }
     CUtensorMap map_w, map_x;
     if (!make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, static_cast<uint64_t>(L.K) / 2, static_cast<uint64_t>(L.O),

@@ -36,6 +36,7 @@ def test_gemm_is_selected_and_matches_oracle(mlxq, oracle, x_dtype):
     layer = DevLayer.from_fixture(mlxq, fx)
     assert layer.linear.kernelFor(T, x_dtype, 0) == "qgemm"
     assert layer.linear.gemmTileTokens(T) == 128 and layer.linear.gemmTileTokens(4) == 0
+    assert layer.linear.gemmTileTokens(129) == 256          # longer batches take the 128-row x 256-token tile
     x = oracle.RNG(77).floats(T * K).reshape(T, K)
     xr = as_dtype(x, x_dtype).float().cpu().numpy()
     got = run(layer, x, T, x_dtype=x_dtype)
