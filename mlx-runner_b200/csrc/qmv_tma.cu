@@ -94,10 +94,18 @@ size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, int sms, TmaPlan& 
             (reinterpret_cast<uintptr_t>(q.part[i].b) & 15u))
             return 0;
     }
-    const long long w_bytes = 8LL * K * bits / 8;
+    // Stage granularity: a whole 16-row block per stage (three copies per block -- a bulk copy costs the issuing
+    // thread ~100 ns, so fewer and larger copies) when every part holds a multiple of 16 rows and four such stages
+    // fit; otherwise 8-row stages (long rows).
+    bool rows16 = q.total_rows >= 16;
+    for (int i = 0; i < q.n_parts; i++) rows16 = rows16 && q.part[i].rows % 16 == 0;
+    const long long row_b = static_cast<long long>(K) * bits / 8;
+    if (rows16 && align_up(static_cast<int>(16 * row_b + 2 * 16 * groups * sbytes), 128) * 4LL > 150 * 1024) rows16 = false;
+    tp.rps = rows16 ? 16 : 8;
+    const long long w_bytes = tp.rps * row_b;
     if (w_bytes > 96 * 1024) return 0;
     tp.w_bytes = static_cast<int>(w_bytes);
-    tp.s_bytes = 8 * groups * sbytes;
+    tp.s_bytes = tp.rps * groups * sbytes;
     tp.stage_bytes = align_up(tp.w_bytes + 2 * tp.s_bytes, 128);
     tp.n_blocks = (q.total_rows + 15) / 16;
     int np = 1;
@@ -125,9 +133,11 @@ size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, int sms, TmaPlan& 
         const int room = (consumers == 8 ? SMEM_HALF : SMEM_BUDGET) - tp.off_stage;
         int ns = room > 0 ? room / tp.stage_bytes : 0;
         if (ns > TMA_MAX_STAGES) ns = TMA_MAX_STAGES;
-        // the ring holds at least the blocks in work, two stages each (see the consumers' double wait), and
-        // the half-size layout is only worth it with two blocks in flight
-        if (ns < 2 * (consumers / ksplit) || (consumers == 8 && ns < 4)) continue;
+        // the ring holds at least the blocks in work (see the consumers' double wait), and the half-size layout
+        // is only worth it with two blocks in flight
+        const int per_block = 16 / tp.rps;
+        const int need = per_block * (consumers / ksplit);      // one block per consumer group in work
+        if (ns < (need > 2 ? need : 2) || (consumers == 8 && ns < 2 * per_block)) continue;
         tp.ns = ns;
         const int per_sm = consumers == 8 ? 2 : 1;
         tp.grid = tp.n_blocks < sms * per_sm ? tp.n_blocks : sms * per_sm;

@@ -41,9 +41,10 @@ __device__ unsigned long long g_tma_trace[148 * 64];
 #endif
 
 struct TmaPlan {
-    int ns;              // ring stages (half blocks)
-    int w_bytes;         // 8 rows of packed weights
-    int s_bytes;         // 8 rows of scales (or of biases)
+    int ns;              // ring stages
+    int rps;             // rows per stage: 16 (a whole block: three copies per block) or 8 (half a block, long rows)
+    int w_bytes;         // a stage's packed weights
+    int s_bytes;         // a stage's scales (or biases)
     int stage_bytes;     // w_bytes + 2 * s_bytes, rounded up to 128
     int off_xsum, off_csum, off_part, off_stage, off_bars;   // shared-memory offsets
     int off_zero;        // 256 bytes of zeros: the B fragment of lanes whose accumulator column is idle in a step
@@ -125,16 +126,17 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         // lands before that only drives the count negative for a moment, the phase cannot complete without
         // the arrival.
         uint32_t n_it = 0;
-        if (lane < 6) {
+        const int nh = 16 / tp.rps;                              // stages per block
+        if (lane < 3 * nh) {
             const int h = lane / 3, j = lane - 3 * h;
             if (lane == 0) TTRACE(1);
             uint32_t it = h;
-            for (int blk = blockIdx.x; blk < tp.n_blocks; blk += gridDim.x, it += 2) {
+            for (int blk = blockIdx.x; blk < tp.n_blocks; blk += gridDim.x, it += nh) {
                 const int st = it % tp.ns;
                 if (it >= static_cast<uint32_t>(tp.ns))
                     mbar_wait(&bars->empty[st], ((it / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
-                // the half's first row, resolved to its layer part (a missing second half re-reads the first)
-                int r = min(blk * 16 + 8 * h, q.total_rows - 8), pi = 0;
+                // the stage's first row, resolved to its layer part (8-row stages: a missing second half re-reads the first)
+                int r = min(blk * 16 + 8 * h, q.total_rows - tp.rps), pi = 0;
                 if (q.n_parts > 1 && r >= q.part[0].rows) {
                     r -= q.part[0].rows; pi = 1;
                     if (q.n_parts > 2 && r >= q.part[1].rows) { r -= q.part[1].rows; pi = 2; }
@@ -153,6 +155,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
             }
             n_it = it - h;
         }
+        n_it = __shfl_sync(0xffffffffu, n_it, 0);
         __syncwarp();
         if (lane == 0) {
             // see every copy of the last ring turn land before leaving (bounded)
@@ -338,7 +341,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         lane_fast = lane_fast && ok0 == ok1;
         f_ok = lane_fast && ok0;
         if (f_ok) {
-            f_soff = tp.w_bytes + 2 * (g * groups + g0);
+            f_soff = 2 * (g * groups + g0);
             f_xoff = c_xc[0][0] * groups + g0;      // the sums themselves exist only after the staging below
         }
     }
@@ -408,10 +411,15 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
     if (ctid == 0) TTRACE(17);
     // the CTA's blocks are dealt to the consumer groups in turn: group `stream` takes blocks stream, stream + n_streams, ...
     for (uint32_t bi = stream; blockIdx.x + static_cast<long long>(bi) * gridDim.x < tp.n_blocks; bi += n_streams) {
-        const uint32_t it = 2 * bi;
-        const int st0 = it % tp.ns, st1 = (it + 1) % tp.ns;
-        const uint8_t* half0 = stages + static_cast<size_t>(st0) * tp.stage_bytes;   // rows 0..7: weights | scales | biases
-        const uint8_t* half1 = stages + static_cast<size_t>(st1) * tp.stage_bytes;   // rows 8..15
+        // the block's stage(s): rows 0..7 and 8..15 with their scale and bias rows
+        const bool two = tp.rps == 8;
+        const uint32_t it = two ? 2 * bi : bi;
+        const int st0 = it % tp.ns, st1 = two ? (it + 1) % tp.ns : st0;
+        const uint8_t* half0 = stages + static_cast<size_t>(st0) * tp.stage_bytes;
+        const uint8_t* half1 = two ? stages + static_cast<size_t>(st1) * tp.stage_bytes : half0 + 8 * row_bytes;
+        const int s_half = two ? 0 : tp.s_bytes / 2;            // one 16-row stage: the second half's scale rows follow the first's
+        const uint8_t* s_ptr[2] = {half0 + tp.w_bytes, (two ? half1 : half0) + tp.w_bytes + s_half};
+        const uint8_t* b_ptr[2] = {s_ptr[0] + tp.s_bytes, s_ptr[1] + tp.s_bytes};
         constexpr int NCH = NP >= 4 ? 1 : 4 / NP;          // independent accumulator chains per pass (eight were no faster)
         float yacc[NP][4], c[NP][NCH][4];
 #pragma unroll
@@ -426,9 +434,9 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         // order: make sure that use has completed first, or its still-open phase would read as this one's
         // parity.  (Uses two ring turns back are complete: this group's last block needed them released.)
         if (n_streams > 1 && it >= static_cast<uint32_t>(tp.ns)) mbar_wait_warp(&bars->full[st0], ((it / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
-        if (n_streams > 1 && it + 1 >= static_cast<uint32_t>(tp.ns)) mbar_wait_warp(&bars->full[st1], (((it + 1) / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
+        if (two && n_streams > 1 && it + 1 >= static_cast<uint32_t>(tp.ns)) mbar_wait_warp(&bars->full[st1], (((it + 1) / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
         mbar_wait_warp(&bars->full[st0], (it / tp.ns) & 1, &bars->abort_flag, p.err);
-        mbar_wait_warp(&bars->full[st1], ((it + 1) / tp.ns) & 1, &bars->abort_flag, p.err);
+        if (two) mbar_wait_warp(&bars->full[st1], ((it + 1) / tp.ns) & 1, &bars->abort_flag, p.err);
         if (kw == 0 && lane == 0 && bi < 6) TTRACE(20 + 4 * bi);
 
         const uint8_t* f0 = half0 + frag_off + s_begin * (4 * LB);
@@ -520,9 +528,8 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                         if (f_ok) {
 #pragma unroll
                             for (int h = 0; h < 2; h++) {
-                                const uint8_t* rows = (h ? half1 : half0) + f_soff;
-                                const uint32_t su = *reinterpret_cast<const uint32_t*>(rows);
-                                const uint32_t bu = *reinterpret_cast<const uint32_t*>(rows + tp.s_bytes);
+                                const uint32_t su = *reinterpret_cast<const uint32_t*>(s_ptr[h] + f_soff);
+                                const uint32_t bu = *reinterpret_cast<const uint32_t*>(b_ptr[h] + f_soff);
                                 float2 sf, bf;
                                 if (q.s_dtype == DT_F16) {
                                     sf = __half22float2(*reinterpret_cast<const __half2*>(&su));
@@ -542,8 +549,8 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
                     const bool ok1 = c_xc[ps][1] >= 0 && g1 >= gmin && g1 < glimit;
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        const uint8_t* srows = (h ? half1 : half0) + tp.w_bytes;      // scales [8][groups], then biases
-                        const uint8_t* brows = srows + tp.s_bytes;
+                        const uint8_t* srows = s_ptr[h];                              // scales [8][groups] of this half
+                        const uint8_t* brows = b_ptr[h];
                         if (pair16 && ok0 && ok1) {
                             const size_t si = static_cast<size_t>(g) * groups + g0;
                             const uint32_t su = *reinterpret_cast<const uint32_t*>(srows + 2 * si);
@@ -578,7 +585,7 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
         if (kw == 0 && lane == 0 && bi < 6) TTRACE(21 + 4 * bi);
         // both half blocks are consumed (weights in registers, scales applied): hand them back
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&bars->empty[st0]); mbar_arrive(&bars->empty[st1]); }
+        if (lane == 0) { mbar_arrive(&bars->empty[st0]); if (two) mbar_arrive(&bars->empty[st1]); }
 
         // deliver the partial sums to the reducer
         const int slot = bi % tp.slots;
