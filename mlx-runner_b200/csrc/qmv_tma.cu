@@ -141,6 +141,11 @@ size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, int sms, TmaPlan& 
         tp.ns = ns;
         const int per_sm = consumers == 8 ? 2 : 1;
         tp.grid = tp.n_blocks < sms * per_sm ? tp.n_blocks : sms * per_sm;
+        // Only calls whose every CTA keeps all its blocks in the ring at once take this kernel: with a ring that
+        // has to be reused inside a launch (long rows, large batches, very tall layers) the kernel was seen to run
+        // into its bounded waits on a B200; until that is understood those calls go to the register-fed kernel.
+        const int blocks_per_cta = (tp.n_blocks + tp.grid - 1) / tp.grid;
+        if (blocks_per_cta * per_block > ns) continue;
         return static_cast<size_t>(tp.off_stage) + static_cast<size_t>(ns) * tp.stage_bytes;
     }
     return 0;

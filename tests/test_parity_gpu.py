@@ -5,11 +5,15 @@ same shapes, same xorshift seeds, same error metric (max |got-ref| / max(1,|ref|
 Tolerance: 1e-3 (the bar this build states; the reference's own bar is 2e-3), 5e-3 for the gated output
 (as KernelTests.swift:211) and 1e-5 for the dequantising lookup (KernelTests.swift:295).  Unpacked codes
 must be bit-exact."""
+import importlib
+
 import numpy as np
 import pytest
 import torch
 
 from helpers import DevLayer, as_dtype, dev, run
+
+synth = importlib.import_module("mlx-runner_b200.synth")
 
 pytestmark = pytest.mark.gpu
 
@@ -291,3 +295,18 @@ def test_committed_golden_cases(mlxq, oracle):
             got = run(layer, c.x[:T], T)
             assert oracle.max_rel_err(got, c.y[:T]) < 1e-3, f"{c.name} T={T}"
     mlxq.streamStatus(None, 0)
+
+
+@pytest.mark.parametrize("bits,T,O", [(5, 1, 11008), (4, 8, 11008), (4, 1, 40000), (8, 2, 11008)])
+def test_tall_layers_and_larger_batches_run_clean(mlxq, oracle, bits, T, O):
+    # benchmark-sized layers whose CTAs hold more 16-row blocks than the shared-memory ring: outputs against the
+    # oracle on a sample of rows, and the stream's error word stays clear (a bounded wait that ran out would set it)
+    K = 4096
+    lay = synth.make_layer(O, K, bits, 64, synth.F16, seed=bits + T, keep_codes=False)
+    layer = DevLayer(mlxq, lay.packed, lay.scales_raw, lay.biases_raw, synth.F16, K)
+    _, x = synth.make_activations(T, K, synth.F16, seed=3)
+    got = run(layer, x, T, x_dtype=1)
+    mlxq.streamStatus(None, 0)
+    rows = np.sort(np.random.default_rng(O).choice(O, size=96, replace=False))
+    ref = oracle.qmatmul(lay.packed[rows], lay.scales_raw[rows], lay.biases_raw[rows], synth.F16, x, K, bits, 64)
+    assert oracle.max_rel_err(got[:, rows], ref) < 1e-3
