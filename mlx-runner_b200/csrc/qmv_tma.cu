@@ -136,16 +136,18 @@ size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, int sms, TmaPlan& 
         // the ring holds at least the blocks in work (see the consumers' double wait), and the half-size layout
         // is only worth it with two blocks in flight
         const int per_block = 16 / tp.rps;
-        const int need = per_block * (consumers / ksplit);      // one block per consumer group in work
-        if (ns < (need > 2 ? need : 2) || (consumers == 8 && ns < 2 * per_block)) continue;
-        tp.ns = ns;
+        const int round = per_block * (consumers / ksplit);     // stages the consumer groups take per round of blocks
         const int per_sm = consumers == 8 ? 2 : 1;
         tp.grid = tp.n_blocks < sms * per_sm ? tp.n_blocks : sms * per_sm;
-        // Only calls whose every CTA keeps all its blocks in the ring at once take this kernel: with a ring that
-        // has to be reused inside a launch (long rows, large batches, very tall layers) the kernel was seen to run
-        // into its bounded waits on a B200; until that is understood those calls go to the register-fed kernel.
         const int blocks_per_cta = (tp.n_blocks + tp.grid - 1) / tp.grid;
-        if (blocks_per_cta * per_block > ns) continue;
+        if (blocks_per_cta * per_block > ns) {
+            // stages are reused inside the launch: a stage must always return to the same consumer group
+            static const bool no_wrap = [] { const char* e = std::getenv("MLXQ_TMA_WRAP"); return e && e[0] == '0'; }();
+            if (no_wrap) continue;                               // MLXQ_TMA_WRAP=0: such calls go to the register-fed kernel
+            ns -= ns % round;
+        }
+        if (ns < round || (consumers == 8 && ns < 2 * per_block)) continue;
+        tp.ns = ns;
         return static_cast<size_t>(tp.off_stage) + static_cast<size_t>(ns) * tp.stage_bytes;
     }
     return 0;

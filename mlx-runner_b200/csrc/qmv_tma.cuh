@@ -430,11 +430,10 @@ qmv_tma_kernel(const MmaParams p, const TmaPlan tp) {
 #pragma unroll
                 for (int k = 0; k < NCH; k++) c[ps][k][i] = 0.0f;
             }
-        // A stage's previous use may have gone to another consumer group, and bulk copies do not land in
-        // order: make sure that use has completed first, or its still-open phase would read as this one's
-        // parity.  (Uses two ring turns back are complete: this group's last block needed them released.)
-        if (n_streams > 1 && it >= static_cast<uint32_t>(tp.ns)) mbar_wait_warp(&bars->full[st0], ((it / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
-        if (two && n_streams > 1 && it + 1 >= static_cast<uint32_t>(tp.ns)) mbar_wait_warp(&bars->full[st1], (((it + 1) / tp.ns) - 1) & 1, &bars->abort_flag, p.err);
+        // (The ring length is a multiple of the stages the consumer groups take per round, so a stage always
+        // comes back to the same group and each group sees its stages' phases in order.  An earlier version let
+        // stages change hands and first waited for the previous use's phase: when the current copy had already
+        // landed, that wait was for a phase of the future and ran into its time limit.)
         mbar_wait_warp(&bars->full[st0], (it / tp.ns) & 1, &bars->abort_flag, p.err);
         if (two) mbar_wait_warp(&bars->full[st1], ((it + 1) / tp.ns) & 1, &bars->abort_flag, p.err);
         if (kw == 0 && lane == 0 && bi < 6) TTRACE(20 + 4 * bi);
