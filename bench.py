@@ -141,6 +141,59 @@ def cpu_sample(seconds_target: float = 12.0):
             "ms_per_call": best * 1e3}
 
 
+def run_sweep(args):
+    """--sweep: the decode matvec over bit widths, group sizes, batch sizes and the two projection shapes of the
+    reference's sweep configuration, as a markdown table on stdout (not the benchmark's JSON line).  Every case
+    runs eight distinct weight sets per step, replayed as a CUDA graph, timed with CUDA events."""
+    import torch
+    mlxq = importlib.import_module("mlx-runner_b200")
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    dev = torch.device("cuda", 0)
+
+    def one(O, K, bits, gs, M, L=8, reps=10):
+        layers, keep = [], []
+        for i in range(L):
+            lay = synth.make_layer(O, K, bits, gs, synth.F16, seed=i, keep_codes=False)
+            w = torch.from_numpy(lay.packed.view(np.int32)).to(dev)
+            sc = torch.from_numpy(lay.scales_raw.view(np.int16)).to(dev).view(torch.float16)
+            bi = torch.from_numpy(lay.biases_raw.view(np.int16)).to(dev).view(torch.float16)
+            keep.append((w, sc, bi))
+            layers.append(mlxq.Linear(w, sc, bi, None, inDim=K))
+        x = torch.randn((M, K), device=dev, dtype=torch.float16)
+        y = torch.empty((L, M, O), device=dev, dtype=torch.float32)
+
+        def step():
+            st = torch.cuda.current_stream()
+            for i, lin in enumerate(layers):
+                lin.encode(st, x, K, y[i], O, M)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        mlxq.streamStatus(None, 0)
+        us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+        return us, alg_bytes(O, K, bits, gs, M) / us / 1e3
+
+    print("| shape (out x in) | bits | group | M | us per launch | GB/s |")
+    print("|---|---|---|---|---|---|")
+    cases = [(11008, 4096, b, 64, m) for b in (2, 3, 4, 5, 6, 8) for m in (1, 8)]
+    cases += [(4096, 11008, 4, 64, m) for m in (1, 8)] + [(11008, 4096, 4, gs, m) for gs in (32, 128) for m in (1, 4)]
+    for O, K, bits, gs, M in cases:
+        us, gbs = one(O, K, bits, gs, M)
+        print(f"| {O} x {K} | {bits} | {gs} | {M} | {us:.1f} | {gbs:.0f} |", flush=True)
+
+
 def run_reference(args):
     """--impl reference: the reference's CPU algorithm (oracle port; the Swift sources cannot be built on
     Linux) on all host cores.  A step is one matvec over one layer of the workload."""
@@ -388,10 +441,13 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM probe")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: rows stored into the peers' windows by the decode kernel (fused) or ncclAllGather after it")
+    ap.add_argument("--sweep", action="store_true", help="print the decode sweep table (bits x group x M) instead of the JSON line")
     ap.add_argument("--no-graph", action="store_true", help="time plain API calls instead of a replayed CUDA graph")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight sets per step (default 16)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
