@@ -112,7 +112,8 @@ size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, int sms, TmaPlan& 
     while (np < p.passes) np *= 2;
     int off = align_up(p.xn * p.xstride * 2, 16);
     tp.off_xsum = off; off += align_up(p.xn * groups * 4, 16);
-    tp.off_csum = off; off += align_up(tokens * (K / 8) * 4, 16);
+    // (16-bit activations get their group sums from shuffles: the per-chunk sums are only staged for fp32 ones)
+    tp.off_csum = off; off += p.split == 1 ? 0 : align_up(tokens * (K / 8) * 4, 16);
     // Two layouts: 16 consumer warps (two groups of 8 working on alternate blocks) on a whole SM, or 8
     // consumer warps with half the shared memory and two CTAs per SM.  The first measured faster on the
     // benchmark shapes (10.7 vs 11.9 us per 11008x4096 4-bit launch) and is the default;
@@ -124,8 +125,8 @@ size_t qmv_tma_plan(int bits, const MmaParams& p, int tokens, int sms, TmaPlan& 
         off = fixed;
         tp.consumers = consumers;
         tp.ksplit = ksplit;
-        tp.slots = TMA_SLOTS;
         tp.rowsum = (tokens == 1 && np == 1) ? 1 : 0;
+        tp.slots = tp.rowsum ? TMA_SLOTS : 4;          // full partial sums are 4 KB per warp: fewer slots leave room for the ring
         tp.off_part = off; off += tp.slots * ksplit * (tp.rowsum ? 16 : np * 128) * 4;
         tp.off_zero = align_up(off, 16); off = tp.off_zero + 256;
         tp.off_bars = align_up(off, 16); off = tp.off_bars + static_cast<int>(sizeof(TmaBars));
