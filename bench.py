@@ -421,7 +421,7 @@ def run_ours(args):
         if cpu:
             out["cpu_baseline"] = cpu
         # DRAM bytes one launch of the decode kernel moved under ncu (dram__bytes_read.sum + dram__bytes_write.sum,
-        # profiles/qmv_tma_b4g64_m1.md); the capture is of this workload's kernel at this shape.
+        # from the capture summarised under profiles/); the capture is of this workload's kernel at this shape.
         out["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH      # every rank runs this shape (weak scaling)
         print(json.dumps(out), flush=True)
     if comm is not None:
