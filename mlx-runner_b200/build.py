@@ -31,7 +31,7 @@ COMMON = ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcom
 UNITS = [("qmv_inst.cu", f"qmv_b{b}.o", [f"-DMLXQ_BITS={b}"]) for b in (2, 3, 4, 5, 6, 8)] + [
     ("aux_kernels.cu", "aux_kernels.o", []),
     ("qmv_mma.cu", "qmv_mma.o", []),
-    ("qmv_tma.cu", "qmv_tma.o", []),
+    ("qmv_pipe.cu", "qmv_pipe.o", []),
     ("qgemm_sm100.cu", "qgemm_sm100.o", []),
     ("api.cu", "api.o", []),
     ("comm.cu", "comm.o", []),

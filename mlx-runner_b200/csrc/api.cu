@@ -16,7 +16,7 @@
 #include "qgemm.cuh"
 #include "qmv.cuh"
 #include "qmv_mma.cuh"
-#include "qmv_tma.cuh"
+#include "qmv_pipe.cuh"
 
 namespace mlxq {
 
@@ -238,13 +238,13 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         p.y = y;
         mp.q = p;
         mp.err = device_error_word(parts[0]->device);
-        // Preferred: the persistent kernel fed by TMA bulk copies (MLXQ_DECODE=mma keeps the register-fed one).
+        // Preferred: the persistent kernel fed by asynchronous copies (MLXQ_DECODE=mma keeps the register-fed one).
         const char* mode = getenv("MLXQ_DECODE");
-        TmaPlan tp;
-        const size_t tsmem = (mode && strcmp(mode, "mma") == 0) || !mp.err ? 0 : qmv_tma_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), tp);
-        if (peer && !tsmem) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
-        cudaError_t err = tsmem ? launch_qmv_tma(parts[0]->bits, mp, tp, tsmem, st)
-                                : launch_qmv_mma(parts[0]->bits, mp, smem, st);
+        PipePlan pp;
+        const size_t rsmem = (mode && strcmp(mode, "mma") == 0) || !mp.err ? 0 : qmv_pipe_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), pp);
+        if (peer && !rsmem) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
+        cudaError_t err = rsmem ? launch_qmv_pipe(parts[0]->bits, mp, pp, rsmem, parts[0]->device, st)
+                                : launch_qmv_mma(parts[0]->bits, mp, smem, parts[0]->device, st);
         if (err != cudaSuccess) return cuda_fail(err, "qmv (tensor-core) launch");
         return MLXQ_OK;
     }
@@ -402,6 +402,11 @@ int mlxq_linear_forward_static(mlxq_linear_t h, mlxq_stream_t stream, const void
         if (need > qgemm_static_capacity())
             return fail(MLXQ_INVALID_ARGUMENT, "%s: T * in_dim * 2 = %llu bytes of staged activations exceed the %zu-byte static scratch; "
                         "split the batch or use mlxq_linear_forward", h->name.c_str(), need, qgemm_static_capacity());
+        const size_t table = qgemm_table_bytes(gemm_layer(h));
+        if (table > qgemm_static_table_capacity())
+            return fail(MLXQ_INVALID_ARGUMENT, "%s: the layer's staged scale table (%zu bytes, out_dim * in_dim / 8 with rows rounded up to 256) "
+                        "exceeds the %zu-byte static scratch; shard the layer or use mlxq_linear_forward", h->name.c_str(), table,
+                        qgemm_static_table_capacity());
         GemmCall c;
         c.x = x; c.x_dtype = x_dtype; c.x_stride = x_stride; c.y = y; c.y_dtype = y_dtype; c.y_stride = y_stride; c.T = T;
         c.err = device_error_word(h->device);

@@ -37,6 +37,9 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
 // The same GEMM with its scratch in a fixed device array instead of pool memory: allocates nothing.
 // Returns cudaErrorInvalidValue (why = "batch exceeds the static scratch") beyond qgemm_static_capacity().
 size_t qgemm_static_capacity();
+// Bytes of the scale/bias table the GEMM stages for this layer, and the room the fixed array has for it.
+size_t qgemm_table_bytes(const GemmLayer& L);
+size_t qgemm_static_table_capacity();
 cudaError_t launch_qgemm_static(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why);
 
 }  // namespace mlxq

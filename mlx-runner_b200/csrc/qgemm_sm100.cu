@@ -1012,6 +1012,8 @@ constexpr size_t STATIC_TABLE_BYTES = 16u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_X_BYTES + STATIC_TABLE_BYTES];
 
 size_t qgemm_static_capacity() { return STATIC_X_BYTES; }
+size_t qgemm_static_table_capacity() { return STATIC_TABLE_BYTES; }
+size_t qgemm_table_bytes(const GemmLayer& L) { return table_bytes(L); }
 
 cudaError_t launch_qgemm_static(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why) {
     *why = "";

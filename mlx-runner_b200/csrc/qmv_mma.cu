@@ -21,24 +21,30 @@ int kb_for(int bits) {
 }
 
 template <int BITS, int NP>
-cudaError_t launch_one(const MmaParams& p, size_t smem, cudaStream_t st) {
-    static std::once_flag once;
-    static cudaError_t attr = cudaSuccess;
-    std::call_once(once, [] {
-        attr = cudaFuncSetAttribute(qmv_mma_kernel<BITS, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    });
-    if (attr != cudaSuccess) return attr;
+cudaError_t launch_one(const MmaParams& p, size_t smem, int device, cudaStream_t st) {
+    // the shared-memory opt-in belongs to one device's context: once per device, with that device current
+    static std::mutex mu;
+    static bool done[64] = {};
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!done[device]) {
+            const cudaError_t e = cudaFuncSetAttribute(qmv_mma_kernel<BITS, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return e;
+            done[device] = true;
+        }
+    }
     const unsigned grid = static_cast<unsigned>((p.q.total_rows + 15) / 16);
     qmv_mma_kernel<BITS, NP><<<grid, MMA_WARPS * 32, smem, st>>>(p);
     return cudaGetLastError();
 }
 
 template <int BITS>
-cudaError_t launch_bits(const MmaParams& p, size_t smem, cudaStream_t st) {
-    if (p.passes <= 1) return launch_one<BITS, 1>(p, smem, st);
-    if (p.passes <= 2) return launch_one<BITS, 2>(p, smem, st);
-    if (p.passes <= 4) return launch_one<BITS, 4>(p, smem, st);
-    if (p.passes <= 8) return launch_one<BITS, 8>(p, smem, st);
+cudaError_t launch_bits(const MmaParams& p, size_t smem, int device, cudaStream_t st) {
+    if (p.passes <= 1) return launch_one<BITS, 1>(p, smem, device, st);
+    if (p.passes <= 2) return launch_one<BITS, 2>(p, smem, device, st);
+    if (p.passes <= 4) return launch_one<BITS, 4>(p, smem, device, st);
+    if (p.passes <= 8) return launch_one<BITS, 8>(p, smem, device, st);
     return cudaErrorNotSupported;
 }
 
@@ -77,14 +83,14 @@ size_t qmv_mma_smem(int K, int gs, int tokens, const MmaParams& p) {
     return total <= 200 * 1024 ? total : 0;
 }
 
-cudaError_t launch_qmv_mma(int bits, const MmaParams& p, size_t smem, cudaStream_t st) {
+cudaError_t launch_qmv_mma(int bits, const MmaParams& p, size_t smem, int device, cudaStream_t st) {
     switch (bits) {
-        case 2: return launch_bits<2>(p, smem, st);
-        case 3: return launch_bits<3>(p, smem, st);
-        case 4: return launch_bits<4>(p, smem, st);
-        case 5: return launch_bits<5>(p, smem, st);
-        case 6: return launch_bits<6>(p, smem, st);
-        case 8: return launch_bits<8>(p, smem, st);
+        case 2: return launch_bits<2>(p, smem, device, st);
+        case 3: return launch_bits<3>(p, smem, device, st);
+        case 4: return launch_bits<4>(p, smem, device, st);
+        case 5: return launch_bits<5>(p, smem, device, st);
+        case 6: return launch_bits<6>(p, smem, device, st);
+        case 8: return launch_bits<8>(p, smem, device, st);
         default: return cudaErrorNotSupported;
     }
 }

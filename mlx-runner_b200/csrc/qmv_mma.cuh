@@ -371,6 +371,6 @@ bool qmv_mma_plan(int bits, int K, int gs, int xn, MmaParams& p);
 // Shared memory the kernel needs for a planned call.
 size_t qmv_mma_smem(int K, int gs, int tokens, const MmaParams& p);
 // Launch (bits, passes) instantiation; returns cudaErrorNotSupported when there is none.
-cudaError_t launch_qmv_mma(int bits, const MmaParams& p, size_t smem, cudaStream_t st);
+cudaError_t launch_qmv_mma(int bits, const MmaParams& p, size_t smem, int device, cudaStream_t st);
 
 }  // namespace mlxq

@@ -25,10 +25,13 @@ def _forward(layer, x_dev, T, static):
     y = torch.full((T, lin.outDim), float("nan"), dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
     held = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()
     (lin.encodeStatic if static else lin.encode)(None, x_dev, lin.inDim, y, lin.outDim, T)
     torch.cuda.synchronize()
     if static:
         assert torch.cuda.memory_allocated() == held       # nothing of torch's was allocated by the call either
+        # the device's free bytes see what torch's counter cannot: a cudaMalloc or a pool growing inside the library
+        assert torch.cuda.mem_get_info()[0] == free_before
     return y.cpu().numpy()
 
 
@@ -61,6 +64,21 @@ def test_static_forward_rejects_batches_beyond_the_array(mlxq):
     with pytest.raises(mlxq.InvalidArgument, match="static scratch"):
         layer.linear.encodeStatic(None, x, K, y, 256, T)
     layer.linear.encodeStatic(None, x, K, y, 256, T - 1)                     # the largest batch that fits
+    mlxq.streamStatus(None, 0)
+
+
+def test_static_forward_rejects_layers_whose_table_exceeds_the_array(mlxq):
+    # the staged scale/bias table takes out_dim * in_dim / 8 bytes: 36864 x 4096 needs 18 MiB, the array has 16
+    O, K, T = 36864, 4096, 32
+    w = torch.zeros((O, K // 8), dtype=torch.int32, device="cuda")
+    s = torch.ones((O, K // 64), dtype=torch.bfloat16, device="cuda")
+    lin = mlxq.Linear(w, s, s, None, inDim=K, name="too_tall")
+    assert lin.kernelFor(T, mlxq.BF16, mlxq.F32) == "qgemm"
+    x = torch.zeros((T, K), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((T, O), dtype=torch.float32, device="cuda")
+    with pytest.raises(mlxq.InvalidArgument, match="scale table"):
+        lin.encodeStatic(None, x, K, y, O, T)
+    lin.encode(None, x, K, y, O, T)                                          # the allocating entry point takes it
     mlxq.streamStatus(None, 0)
 
 
