@@ -26,18 +26,13 @@ void unit_for(int bits, int& lb, int& kb) {
 
 int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
-int env_int(const char* name) {
-    const char* e = std::getenv(name);
-    return e ? std::atoi(e) : 0;
-}
-
 // MLXQ_PDL=0 launches without the programmatic-dependent-launch attribute (see the kernel's prologue).
 bool pdl_enabled() {
     static const bool v = [] { const char* e = std::getenv("MLXQ_PDL"); return !(e && e[0] == '0'); }();
     return v;
 }
 
-template <int BITS, int NP, int UNR>
+template <int BITS, int NP, int UNR, int GS>
 cudaError_t launch_one(const MmaParams& p, const PipePlan& pp, size_t smem, int device, cudaStream_t st) {
     // The shared-memory opt-in is an attribute of the function in one device's context: once per device, with
     // that device current (the caller has selected it).
@@ -47,7 +42,7 @@ cudaError_t launch_one(const MmaParams& p, const PipePlan& pp, size_t smem, int 
     {
         std::lock_guard<std::mutex> lk(mu);
         if (!done[device]) {
-            const cudaError_t e = cudaFuncSetAttribute(qmv_pipe_kernel<BITS, NP, UNR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_WHOLE);
+            const cudaError_t e = cudaFuncSetAttribute(qmv_pipe_kernel<BITS, NP, UNR, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_WHOLE);
             if (e != cudaSuccess) return e;
             done[device] = true;
         }
@@ -62,14 +57,18 @@ cudaError_t launch_one(const MmaParams& p, const PipePlan& pp, size_t smem, int 
     la[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = la;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, qmv_pipe_kernel<BITS, NP, UNR>, p, pp);
+    return cudaLaunchKernelEx(&cfg, qmv_pipe_kernel<BITS, NP, UNR, GS>, p, pp);
 }
 
 template <int BITS, int UNR>
 cudaError_t launch_np(const MmaParams& p, const PipePlan& pp, size_t smem, int device, cudaStream_t st) {
-    if (p.passes <= 1) return launch_one<BITS, 1, UNR>(p, pp, smem, device, st);
-    if (p.passes <= 2) return launch_one<BITS, 2, UNR>(p, pp, smem, device, st);
-    if (p.passes <= 4) return launch_one<BITS, 4, UNR>(p, pp, smem, device, st);
+    // the one-token kernels with the column plan folded in at compile time
+    if (pp.special == 32) return launch_one<BITS, 1, UNR, 32>(p, pp, smem, device, st);
+    if (pp.special == 64) return launch_one<BITS, 1, UNR, 64>(p, pp, smem, device, st);
+    if (pp.special == 128) return launch_one<BITS, 1, UNR, 128>(p, pp, smem, device, st);
+    if (p.passes <= 1) return launch_one<BITS, 1, UNR, 0>(p, pp, smem, device, st);
+    if (p.passes <= 2) return launch_one<BITS, 2, UNR, 0>(p, pp, smem, device, st);
+    if (p.passes <= 4) return launch_one<BITS, 4, UNR, 0>(p, pp, smem, device, st);
     return cudaErrorNotSupported;
 }
 
@@ -104,11 +103,12 @@ size_t qmv_pipe_plan(int bits, const MmaParams& p, int tokens, int sms, PipePlan
     const int slot_bytes = 2 * 32 * lb + 4 * 32 * 4;
     pp.xstride = K + 8;
     const int warps = PIPE_WARPS;
-    // K split: the group size that leaves the longest-working warp the least to do, an exchange counted as one step
+    // K split: the group size that leaves the longest-working warp the least to do
     const int cta_blocks = (pp.n_blocks + pp.grid - 1) / pp.grid;
     int best_ks = 1;
     long long best_cost = -1;
-    for (int ks = 1; ks <= warps && ks <= nblk; ks *= 2) {
+    for (int ks = 1; ks <= warps && ks <= nblk && ks <= 16; ks *= 2) {
+        if (warps % ks != 0 || (ks > 1 && warps / ks > 15)) continue;      // one named barrier per group
         int slice = 0;
         for (int kw = 0; kw < ks; kw++) {
             const int a = ((nblk * kw) / ks) << p.spg_shift, b = ((nblk * (kw + 1)) / ks) << p.spg_shift;
@@ -116,12 +116,10 @@ size_t qmv_pipe_plan(int bits, const MmaParams& p, int tokens, int sms, PipePlan
         }
         const int n_groups = warps / ks;
         const long long rounds = (cta_blocks + n_groups - 1) / n_groups;
-        const long long cost = rounds * (slice + 1);        // (slices of an odd number of steps run the loop that is not unrolled)
+        const long long cost = rounds * (slice + 3);        // (measured: ending a block and meeting the group costs about three steps)
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_ks = ks; }
     }
     pp.ks = best_ks;
-    const int forced = env_int("MLXQ_PIPE_KS");
-    if (forced > 0 && forced <= warps && forced <= nblk && (forced & (forced - 1)) == 0) pp.ks = forced;
     pp.ks_shift = 0;
     while ((1 << pp.ks_shift) < pp.ks) pp.ks_shift++;
     pp.base_blocks = pp.n_blocks / pp.grid;
@@ -150,6 +148,7 @@ size_t qmv_pipe_plan(int bits, const MmaParams& p, int tokens, int sms, PipePlan
             pairs = pairs && (c0 & 255) == (c1 & 255) && g1 == g0 + 1 && (g0 & 1) == 0 && g0 == static_cast<int>((f0 >> 8) & 255);
         }
     pp.async_sb = pairs ? 1 : 0;
+    pp.special = (tokens == 1 && p.split == 1 && p.xn == 1 && pp.async_sb && pp.rowsum && (q.gs == 32 || q.gs == 64 || q.gs == 128)) ? q.gs : 0;
     int off = align_up(p.xn * pp.xstride * 2, 16);
     pp.off_xsum = off; off += align_up(p.xn * groups * 4, 16);
     pp.off_zero = off; off += PIPE_ZERO_BYTES;

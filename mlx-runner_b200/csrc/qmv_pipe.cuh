@@ -40,6 +40,7 @@ struct PipePlan {
     int off_part;        // partial sums [groups of warps][2][ks][16 * tokens] floats
     int off_ring;        // per warp: depth slots of 2 x 32 lanes x lane bytes, then 4 x 32 x 4 bytes of (scale, bias) pairs
     int rowsum;          // 1: one token in one accumulator set -- partials come from two shuffles instead of the tile
+    int special;         // 32 / 64 / 128: the one-token kernel compiled for that group size serves the call; 0: the general one
     int async_sb;        // 1: the drains' (scale, bias) pairs travel through the ring (see pipe_col_pairs)
     // What accumulator column n of pass ps stands for (the column plan of qmv_mma.cuh, worked out once on the host):
     // bits 0-7 staged activation column (255: none), 8-15 group offset inside the cycle block, 16-19 cycle position,
@@ -135,20 +136,33 @@ __device__ __forceinline__ void stage8v(__half* col, int k, const float (&v)[8])
     }
 }
 
-template <int BITS, int NP, int UNR>
+constexpr int pipe_log2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
+
+// GS = 0: any call, the column plan is read from the launch parameters.  GS = 32, 64, 128: the one-token call with
+// 16-bit activations and 16-bit scales at that group size -- the plan is then known at compile time (one pass, a
+// drain cycle of eight consecutive groups, the lane's two accumulator columns are groups 2t and 2t + 1 of it, the
+// pairs travel through the ring), and most of the bookkeeping below folds away.
+template <int BITS, int NP, int UNR, int GS>
 __global__ void __launch_bounds__(PIPE_WARPS * 32, 1)
 qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ PipePlan pp) {
     using U = MmaUnit<BITS>;
     constexpr int LB = U::LB, CL = U::CL, KB = U::KB, NW = U::NW, NM = U::NM;
+    constexpr bool SP = GS != 0;
+    static_assert(!SP || NP == 1, "the one-token plan has one pass");
+    constexpr int SP_GSH = !SP ? 0 : (KB > GS ? pipe_log2(KB / GS) : 0);      // log2(groups per step)
+    constexpr int SP_SPG = !SP ? 0 : (GS > KB ? pipe_log2(GS / KB) : 0);      // log2(steps per group)
+    constexpr int SP_CY = !SP ? 1 : ((8 >> SP_GSH) > 0 ? (8 >> SP_GSH) : 1);  // group blocks per drain cycle
     constexpr int NT = PIPE_WARPS * 32;
     constexpr int DEPTH = PIPE_DEPTH;
     constexpr uint32_t SB_OFF = 2 * 32 * LB;                   // (scale, bias) pairs follow the weights in a slot
     constexpr uint32_t SLOT = SB_OFF + 4 * 32 * 4;
     extern __shared__ __align__(128) uint8_t smem_pipe[];
     const QmvParams& q = p.q;
-    const int K = q.K, gs_shift = q.gs_shift;
+    const int K = q.K, gs_shift = SP ? pipe_log2(GS) : q.gs_shift;
     const int groups = K >> gs_shift;
-    const int sbytes = dtype_size(q.s_dtype);
+    const int sbytes = SP ? 2 : dtype_size(q.s_dtype);
+    const int T = SP ? 1 : q.T, xn = SP ? 1 : p.xn, split = SP ? 1 : p.split;
+    const bool rowsum = SP ? true : pp.rowsum != 0;
     __half* xs = reinterpret_cast<__half*>(smem_pipe);                                   // [xn][xstride]
     float* xsum = reinterpret_cast<float*>(smem_pipe + pp.off_xsum);                     // [xn][groups]
     float* part = reinterpret_cast<float*>(smem_pipe + pp.off_part);
@@ -167,12 +181,12 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     if (threadIdx.x < PIPE_ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(smem_pipe + pp.off_zero)[threadIdx.x] = 0u;
 
     // geometry of the column plan (see qmv_mma.cuh)
-    const int gsh = p.gstep_shift, G = 1 << gsh, CY = p.cycle, spg_shift = p.spg_shift;
-    const int cols_per_cycle = p.xn << gsh;
+    const int gsh = SP ? SP_GSH : p.gstep_shift, G = 1 << gsh, CY = SP ? SP_CY : p.cycle, spg_shift = SP ? SP_SPG : p.spg_shift;
+    const int cols_per_cycle = xn << gsh;
     const int cyc_mask = CY - 1;
     const int dmask = (CY << spg_shift) - 1;                   // a drain closes every (dmask + 1) steps
     // this warp's place: group `gi` of the CTA, slice `kw` of K (cut at group boundaries)
-    const int ks = pp.ks, gi = warp >> pp.ks_shift, kw = warp & (ks - 1), n_groups = PIPE_WARPS >> pp.ks_shift;
+    const int ks = pp.ks, gi = warp >> pp.ks_shift, kw = warp & (ks - 1), n_groups = PIPE_WARPS >> pp.ks_shift;   // (warps per CTA are a multiple of ks)
     const int nblk = steps_total >> spg_shift;
     const int s_begin = ((nblk * kw) >> pp.ks_shift) << spg_shift;
     const int s_end = ((nblk * (kw + 1)) >> pp.ks_shift) << spg_shift;
@@ -183,7 +197,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     const uint32_t ring = smem_u32(smem_pipe + pp.off_ring) + warp * (DEPTH * SLOT) + (LB == 16 ? lane * 16 : lane * 8);
     const uint32_t ring_end = ring + DEPTH * SLOT;
     const uint32_t sb_delta = SB_OFF + lane * 4 - (LB == 16 ? lane * 16 : lane * 8);    // from there to the lane's first pair cell
-    const uint32_t zaddr = smem_u32(smem_pipe + pp.off_zero);
+    const uint32_t zaddr0 = smem_u32(smem_pipe + pp.off_zero);
 
     const int run_grp_a = ((t * CL + mma_code_offset<BITS>(0)) >> gs_shift) & (G - 1);
     const int run_grp_b = ((t * CL + mma_code_offset<BITS>(NM / 2)) >> gs_shift) & (G - 1);
@@ -192,20 +206,20 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     int c_xc[NP][2], c_goff[NP][2];
 #pragma unroll
     for (int ps = 0; ps < NP; ps++) {
-        const uint32_t ce = pp.col[ps][g];                      // the column this lane feeds as B (column n = g)
-        const int xc = ce & 255, cyc = (ce >> 16) & 15, grp = (ce >> 20) & 15;
-        const bool valid = xc != 255;
+        const uint32_t ce = SP ? 0u : pp.col[ps][g];            // the column this lane feeds as B (column n = g)
+        const int xc = SP ? 0 : ce & 255, cyc = SP ? g >> SP_GSH : (ce >> 16) & 15, grp = SP ? g & ((1 << SP_GSH) - 1) : (ce >> 20) & 15;
+        const bool valid = SP ? (g >> SP_GSH) < SP_CY : xc != 255;
         baddr[ps] = smem_u32(xs) + ((valid ? xc : 0) * pp.xstride + t * CL) * 2;
         b_on_a[ps] = (valid && grp == run_grp_a) ? cyc : -1;
         b_on_b[ps] = (valid && grp == run_grp_b) ? cyc : -1;
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
-            const uint32_t cc = pp.col[ps][2 * t + ci];         // the lane's accumulator columns 2t, 2t + 1
-            c_xc[ps][ci] = (cc & 255) == 255 ? -1 : static_cast<int>(cc & 255);
-            c_goff[ps][ci] = (cc >> 8) & 255;
+            const uint32_t cc = SP ? 0u : pp.col[ps][2 * t + ci];   // the lane's accumulator columns 2t, 2t + 1
+            c_xc[ps][ci] = SP ? (((2 * t + ci) >> SP_GSH) < SP_CY ? 0 : -1) : (cc & 255) == 255 ? -1 : static_cast<int>(cc & 255);
+            c_goff[ps][ci] = SP ? 2 * t + ci : (cc >> 8) & 255;
         }
     }
-    const bool async_sb = pp.async_sb != 0;
+    const bool async_sb = SP ? true : pp.async_sb != 0;
     const int pair_off = c_goff[0][0];
 
     // the lane's row g + 8h of block `blk`, resolved to a layer part (rows past the end read the last row)
@@ -222,7 +236,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     // ---- the copy stream: this warp's (block, step) pairs in order, DEPTH of them in flight ------------------------
     // block j of the CTA is blockIdx.x + j * gridDim.x; group gi takes j = gi, gi + n_groups, ...
     const int cta_blocks = pp.base_blocks + (static_cast<int>(blockIdx.x) < pp.extra_blocks ? 1 : 0);
-    const int my_blocks = cta_blocks > gi ? ((cta_blocks - 1 - gi) >> (4 - pp.ks_shift)) + 1 : 0;
+    const int my_blocks = cta_blocks > gi ? (cta_blocks - 1 - gi) / n_groups + 1 : 0;
     const int blk_stride = n_groups * gridDim.x;
     int l_left = my_blocks * nsteps;                           // steps not yet issued
     int l_s = s_begin, l_blk = blockIdx.x + gi * gridDim.x;
@@ -242,43 +256,36 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             }
         }
     };
-    // copies of step (cursor + i) into the slot `i` slots past `dst`, one commit group
-    auto issue_at = [&](uint32_t dst, auto ic) {
-        constexpr int i = decltype(ic)::value;
-        if (l_left > i) {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
+    // copies of the UNR steps under the load cursor into the slots that start at `dst`, one commit group; moves the cursor on
+    auto issue_turn = [&](uint32_t dst) {
+        if (l_left > 0) {
+            static_for<0, UNR, 1>([&](auto ic) {
+                constexpr int i = decltype(ic)::value;
                 if constexpr (LB == 16) {
-                    if (h == 0) cp_async16<i * SLOT, i * 4 * LB>(dst, l_w[0]);
-                    else cp_async16<i * SLOT + 512, i * 4 * LB>(dst, l_w[1]);
+                    cp_async16<i * SLOT, i * 4 * LB>(dst, l_w[0]);
+                    cp_async16<i * SLOT + 512, i * 4 * LB>(dst, l_w[1]);
                 } else {
                     // 24 or 40 bytes per lane as 8-byte pieces; piece k of all lanes forms one 256-byte row of cells
                     static_for<0, LB / 8, 1>([&](auto kc) {
                         constexpr int k = decltype(kc)::value;
-                        if (h == 0) cp_async8<i * SLOT + k * 256, i * 4 * LB + 8 * k>(dst, l_w[0]);
-                        else cp_async8<i * SLOT + (LB / 8 + k) * 256, i * 4 * LB + 8 * k>(dst, l_w[1]);
+                        cp_async8<i * SLOT + k * 256, i * 4 * LB + 8 * k>(dst, l_w[0]);
+                        cp_async8<i * SLOT + (LB / 8 + k) * 256, i * 4 * LB + 8 * k>(dst, l_w[1]);
                     });
                 }
-            }
-            const int ls = l_s + i;
-            if (async_sb && ((((ls + 1) & dmask) == 0) || ls + 1 == s_end)) {
-                // the step closes a drain cycle: the pair (g0, g0 + 1) is fetched when either group lies inside this
-                // warp's slice up to this step
-                const int g0 = (((ls & ~dmask) * KB) >> gs_shift) + pair_off;
-                if (c_xc[0][0] >= 0 && g0 + 1 >= gmin && g0 + 1 < groups && g0 < (((ls + 1) * KB) >> gs_shift)) {
-                    const uint32_t d = dst + sb_delta;
-                    cp_async4<i * SLOT>(d, l_sp[0] + 2 * g0);
-                    cp_async4<i * SLOT + 128>(d, l_bp[0] + 2 * g0);
-                    cp_async4<i * SLOT + 256>(d, l_sp[1] + 2 * g0);
-                    cp_async4<i * SLOT + 384>(d, l_bp[1] + 2 * g0);
+                const int ls = l_s + i;
+                if (async_sb && ((((ls + 1) & dmask) == 0) || ls + 1 == s_end)) {
+                    // the step closes a drain cycle: the pair (g0, g0 + 1) is fetched when either group lies inside this
+                    // warp's slice up to this step
+                    const int g0 = (((ls & ~dmask) * KB) >> gs_shift) + pair_off;
+                    if (c_xc[0][0] >= 0 && g0 + 1 >= gmin && g0 + 1 < groups && g0 < (((ls + 1) * KB) >> gs_shift)) {
+                        const uint32_t d = dst + sb_delta;
+                        cp_async4<i * SLOT>(d, l_sp[0] + 2 * g0);
+                        cp_async4<i * SLOT + 128>(d, l_bp[0] + 2 * g0);
+                        cp_async4<i * SLOT + 256>(d, l_sp[1] + 2 * g0);
+                        cp_async4<i * SLOT + 384>(d, l_bp[1] + 2 * g0);
+                    }
                 }
-            }
-        }
-        cp_commit();
-    };
-    // moves the load cursor UNR steps on
-    auto advance = [&]() {
-        if (l_left > 0) {
+            });
             l_left -= UNR; l_s += UNR;
             l_w[0] += UNR * 4 * LB; l_w[1] += UNR * 4 * LB;
             if (l_s == s_end) {
@@ -286,13 +293,11 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                 if (l_left > 0) load_rows(l_blk);
             }
         }
+        cp_commit();
     };
     if (l_left > 0) load_rows(l_blk);
 #pragma unroll
-    for (int gq = 0; gq < DEPTH / UNR; gq++) {
-        static_for<0, UNR, 1>([&](auto ic) { issue_at(ring + gq * (UNR * SLOT), ic); });
-        advance();
-    }
+    for (int gq = 0; gq < DEPTH / UNR; gq++) issue_turn(ring + gq * (UNR * SLOT));
 
     // ---- the activations: nothing before this line reads x, e or writes y --------------------------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -305,18 +310,18 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         // staged once per CTA: fp16, permuted and pre-scaled to match the A registers (see qmv_mma.cuh), eight
         // values per thread and turn.  The chunks of a group sit in consecutive lanes, so the per-group sums come
         // from a few shuffles, in a fixed order.
-        const int cpr = K >> 3, total_chunks = q.T * cpr;
+        const int cpr = K >> 3, total_chunks = T * cpr;
         const int cpg = 1 << (gs_shift - 3);
         for (int base = 0; base < total_chunks; base += NT) {
             const int idx = base + threadIdx.x;
-            const int tok = q.T == 1 ? 0 : pp.cpr_shift >= 0 ? idx >> pp.cpr_shift : idx / cpr, k = (idx - tok * cpr) * 8;
+            const int tok = T == 1 ? 0 : pp.cpr_shift >= 0 ? idx >> pp.cpr_shift : idx / cpr, k = (idx - tok * cpr) * 8;
             float sum = 0.0f;
             if (idx < total_chunks) {
                 float v[8];
                 load8_coherent(q.x, q.x_dtype, static_cast<size_t>(tok) * q.x_stride + k, v);
 #pragma unroll
                 for (int i = 0; i < 8; i++) sum += v[i];
-                if (p.split == 1) {
+                if (split == 1) {
                     stage8v<BITS>(xs + static_cast<size_t>(tok) * pp.xstride, k, v);
                 } else {
                     float hi[8], lo[8];
@@ -329,7 +334,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             for (int o = 1; o < cpg; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             if (idx < total_chunks && (idx & (cpg - 1)) == 0) {
                 const int gidx = k >> gs_shift;
-                if (p.split == 1) {
+                if (split == 1) {
                     xsum[tok * groups + gidx] = sum;
                 } else {
                     xsum[(2 * tok) * groups + gidx] = sum;          // the lo column of an fp32 token carries no bias term
@@ -339,8 +344,13 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         }
     }
     __syncthreads();
+    // (from here on the staged activations are read with loads the compiler may move: tie their addresses to this point)
+    uint32_t zaddr = zaddr0;
+    asm volatile("" : "+r"(zaddr) :: "memory");
+#pragma unroll
+    for (int ps = 0; ps < NP; ps++) asm volatile("" : "+r"(baddr[ps]) :: "memory");
 
-    const int per_tok = p.split << gsh;
+    const int per_tok = split << gsh;
     constexpr int NCH = NP >= 4 ? 1 : 4 / NP;          // independent accumulator chains per pass
     float yacc[NP][4], c[NP][NCH][4];
 #pragma unroll
@@ -352,6 +362,9 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             for (int k = 0; k < NCH; k++) c[ps][k][i] = 0.0f;
         }
 
+    // partial sums of this warp's group: two slots (the block's parity) of ks x [16 rows x tokens] floats
+    const int par_floats = ks * 16 * T;
+    float* part_g = part + gi * 2 * par_floats;
     uint32_t c_src = ring;                                      // ring slot of the step in work
     int c_blk = blockIdx.x + gi * gridDim.x;
     for (int bj = 0; bj < my_blocks; bj++, c_blk += blk_stride) {
@@ -370,34 +383,40 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         }
         uint32_t koff2 = s_begin * (KB * 2);                    // byte offset of the step's codes inside a staged column
         for (int s0 = s_begin; s0 < s_end; s0 += UNR, koff2 += UNR * KB * 2) {
+            // the turn's UNR steps have landed: their words (and, for steps that close a drain cycle, the pairs) to registers
+            asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH / UNR - 1) : "memory");
+            uint32_t w[UNR][2][NW];
+            uint32_t sbv[UNR][4];
             static_for<0, UNR, 1>([&](auto ic) {
                 constexpr int i = decltype(ic)::value;
-                const int s = s0 + i;
-                asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
-                uint32_t w[2][NW];
                 if constexpr (LB == 16) {
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
-                                 : "=r"(w[0][0]), "=r"(w[0][1]), "=r"(w[0][2]), "=r"(w[0][3]) : "r"(c_src), "n"(i * SLOT));
+                                 : "=r"(w[i][0][0]), "=r"(w[i][0][1]), "=r"(w[i][0][2]), "=r"(w[i][0][3]) : "r"(c_src), "n"(i * SLOT));
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
-                                 : "=r"(w[1][0]), "=r"(w[1][1]), "=r"(w[1][2]), "=r"(w[1][3]) : "r"(c_src), "n"(i * SLOT + 512));
+                                 : "=r"(w[i][1][0]), "=r"(w[i][1][1]), "=r"(w[i][1][2]), "=r"(w[i][1][3]) : "r"(c_src), "n"(i * SLOT + 512));
                 } else {
                     static_for<0, LB / 8, 1>([&](auto kc) {
                         constexpr int k = decltype(kc)::value;
                         asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];"
-                                     : "=r"(w[0][2 * k]), "=r"(w[0][2 * k + 1]) : "r"(c_src), "n"(i * SLOT + k * 256));
+                                     : "=r"(w[i][0][2 * k]), "=r"(w[i][0][2 * k + 1]) : "r"(c_src), "n"(i * SLOT + k * 256));
                         asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];"
-                                     : "=r"(w[1][2 * k]), "=r"(w[1][2 * k + 1]) : "r"(c_src), "n"(i * SLOT + (LB / 8 + k) * 256));
+                                     : "=r"(w[i][1][2 * k]), "=r"(w[i][1][2 * k + 1]) : "r"(c_src), "n"(i * SLOT + (LB / 8 + k) * 256));
                     });
                 }
-                const bool drain = ((s + 1) & dmask) == 0 || s + 1 == s_end;
-                uint32_t sbv[4] = {0u, 0u, 0u, 0u};
-                if (async_sb && drain) {
+                const int s = s0 + i;
+                sbv[i][0] = sbv[i][1] = sbv[i][2] = sbv[i][3] = 0u;
+                if (async_sb && (((s + 1) & dmask) == 0 || s + 1 == s_end)) {
                     const uint32_t d = c_src + sb_delta;
-                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[0]) : "r"(d), "n"(i * SLOT));
-                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[1]) : "r"(d), "n"(i * SLOT + 128));
-                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[2]) : "r"(d), "n"(i * SLOT + 256));
-                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[3]) : "r"(d), "n"(i * SLOT + 384));
+                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[i][0]) : "r"(d), "n"(i * SLOT));
+                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[i][1]) : "r"(d), "n"(i * SLOT + 128));
+                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[i][2]) : "r"(d), "n"(i * SLOT + 256));
+                    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[i][3]) : "r"(d), "n"(i * SLOT + 384));
                 }
+            });
+            static_for<0, UNR, 1>([&](auto ic) {
+                constexpr int i = decltype(ic)::value;
+                const int s = s0 + i;
+                const bool drain = ((s + 1) & dmask) == 0 || s + 1 == s_end;
                 const int cyc_s = (s >> spg_shift) & cyc_mask;
                 // lanes whose accumulator column belongs to another group (or cycle) multiply by zeros: they read
                 // them from a zeroed patch of shared memory, so the loads need no branch
@@ -410,23 +429,22 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                 static_for<0, NM, 2>([&](auto jc) {
                     constexpr int j = decltype(jc)::value;
                     uint32_t a00, a01, a02, a03, a10, a11, a12, a13;
-                    a_regs<BITS>(w[0], j, a00, a02);
-                    a_regs<BITS>(w[1], j, a01, a03);
-                    a_regs<BITS>(w[0], j + 1, a10, a12);
-                    a_regs<BITS>(w[1], j + 1, a11, a13);
+                    a_regs<BITS>(w[i][0], j, a00, a02);
+                    a_regs<BITS>(w[i][1], j, a01, a03);
+                    a_regs<BITS>(w[i][0], j + 1, a10, a12);
+                    a_regs<BITS>(w[i][1], j + 1, a11, a13);
 #pragma unroll
                     for (int ps = 0; ps < NP; ps++) {
+                        // (not volatile: the staged activations do not change after the barrier that follows the staging,
+                        // and the addresses are made to depend on that barrier, so the compiler may schedule these freely)
                         uint4 bv;
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
-                                     : "=r"(bv.x), "=r"(bv.y), "=r"(bv.z), "=r"(bv.w)
-                                     : "r"(j < NM / 2 ? pa[ps] : pb[ps]), "n"(8 * j + i * KB * 2));
+                        asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
+                            : "=r"(bv.x), "=r"(bv.y), "=r"(bv.z), "=r"(bv.w)
+                            : "r"(j < NM / 2 ? pa[ps] : pb[ps]), "n"(8 * j + i * KB * 2));
                         mma16816(c[ps][(j / 2) % NCH], a00, a01, a02, a03, bv.x, bv.y);
                         mma16816(c[ps][(j / 2 + (NCH > 1 ? NCH / 2 : 0)) % NCH], a10, a11, a12, a13, bv.z, bv.w);
                     }
                 });
-                // the slot's words are in registers (the MMAs above have consumed them): refill it with the step that is
-                // DEPTH ahead
-                issue_at(c_src, ic);
                 if (drain) {
                     // end of a group block that closes the cycle (or the warp's range): scale and bias in fp32
                     const int gbase = ((s & ~dmask) * KB) >> gs_shift;
@@ -451,7 +469,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                                 const float2 xv = *reinterpret_cast<const float2*>(xsum + c_xc[ps][0] * groups + g0);
 #pragma unroll
                                 for (int h = 0; h < 2; h++) {
-                                    const uint32_t su = sbv[2 * h], bu = sbv[2 * h + 1];
+                                    const uint32_t su = sbv[i][2 * h], bu = sbv[i][2 * h + 1];
                                     float2 sf, bf;
                                     if (q.s_dtype == DT_F16) {
                                         sf = __half22float2(*reinterpret_cast<const __half2*>(&su));
@@ -481,14 +499,15 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                     }
                 }
             });
-            advance();
+            // the turn's slots are in registers: refill them with the steps that are DEPTH ahead
+            issue_turn(c_src);
             c_src += UNR * SLOT;
             if (c_src == ring_end) c_src = ring;
         }
         // ---- end of a block: this warp's partial sums, compact [16 rows][tokens], to the group's first warp ----------
-        float* slot_base = part + static_cast<size_t>((gi * 2 + (bj & 1)) * ks) * (16 * q.T);
-        float* mine = slot_base + static_cast<size_t>(kw) * (16 * q.T);
-        if (pp.rowsum) {
+        float* slot_base = part_g + ((bj & 1) ? par_floats : 0);
+        float* mine = slot_base + kw * (16 * T);
+        if (rowsum) {
             // one token: the eight accumulator columns of a row all belong to it -- add them across the quad
             float lo = yacc[0][0] + yacc[0][1], hi = yacc[0][2] + yacc[0][3];
             lo += __shfl_xor_sync(0xffffffffu, lo, 1); hi += __shfl_xor_sync(0xffffffffu, hi, 1);
@@ -503,7 +522,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                 for (int i = 0; i < 4; i++)
                     scr[(ps * 16 + g + 8 * (i >> 1)) * 9 + 2 * t + (i & 1)] = yacc[ps][i];
             __syncwarp();
-            for (int idx = lane; idx < 16 * q.T; idx += 32) {
+            for (int idx = lane; idx < 16 * T; idx += 32) {
                 const int tok = idx >> 4, r = idx & 15;
                 float v = 0.0f;
                 for (int cyc = 0; cyc < CY; cyc++) {
@@ -526,11 +545,11 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         if (ks > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(ks * 32) : "memory");
         else __syncwarp();
         if (kw == 0) {
-            for (int idx = lane; idx < 16 * q.T; idx += 32) {
+            for (int idx = lane; idx < 16 * T; idx += 32) {
                 const int tok = idx >> 4, r = idx & 15;
                 const int row = c_blk * 16 + r;
                 float v = 0.0f;
-                for (int wv = 0; wv < ks; wv++) v += slot_base[wv * (16 * q.T) + idx];
+                for (int wv = 0; wv < ks; wv++) v += slot_base[wv * (16 * T) + idx];
                 if (row < q.total_rows) {
                     int pr = row, pi = 0;
                     if (q.n_parts > 1 && pr >= q.part[0].rows) {
