@@ -4,25 +4,28 @@ prefill dequant-GEMM TFLOP/s reported beside it.
 
     python bench.py --gpus N --steps K --warmup W            # this library (one process per GPU under torchrun)
     python bench.py --impl reference --steps K --warmup W    # the reference's CPU algorithm on the host cores
+    python bench.py --config c5 [--bits 6|8] [--batch B]     # vocabulary-sized head, rows split over the ranks
+    python bench.py --config c4 [--batch B]                  # projection walk of a 36-layer transformer, rows split
 
-Workload (N = 1): the 4-bit group-64 matvec of the bit-width x group sweep, W out=11008 x in=4096, M = 1,
-fp16 activations, fp32 output.  One step = one pass over LAYERS distinct weight sets (LAYERS x 25.4 MB =
-406 MB, larger than the 126 MB L2, so every launch streams its weights from HBM), i.e. LAYERS launches.
-value = algorithmic bytes (packed codes + scales + biases + x + y) per second.
+Default workload (N = 1): the 4-bit group-64 matvec of the bit-width x group sweep, W out=11008 x in=4096, M = 1,
+fp16 activations, fp32 output.  One step = PASSES passes over LAYERS distinct weight sets (LAYERS x 25.4 MB =
+406 MB, larger than the 126 MB L2, so every launch streams its weights from HBM), i.e. PASSES x LAYERS launches
+and at least 5 ms of device time.  value = algorithmic bytes (packed codes + scales + biases + x + y) per second.
+N > 1 (weak scaling): every rank holds its own 11008-row shard of a (N x 11008)-row projection; a step is the
+same, each launch followed by the gather of the fp32 output slices over NVLink.
 
-N > 1 (weak scaling): every rank holds its own 11008-row shard of a (N x 11008)-row projection; a step
-is the same pass, each launch followed by the all-gather of the fp32 output slices over NVLink.
+--config c4 / c5 are strong scaling: the fixed layers are split by output rows over the N ranks and every call
+ends with the gather; the JSON line then also carries the kernel-only time of the same step.
 
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
 import argparse
-import ctypes
 import importlib
+import importlib.util
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -33,8 +36,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 O_ROWS, K_COLS, BITS, GS = 11008, 4096, 4, 64
-LAYERS = 16          # distinct weight sets per step; --layers overrides it (profiling runs use fewer)
-NCU_DRAM_BYTES_PER_LAUNCH = 25442048     # ncu capture of the decode kernel at this shape, see profiles/
+LAYERS = 16          # distinct weight sets per pass; --layers overrides it (profiling runs use fewer)
+PASSES = 40          # passes per step: 640 launches, ~5 ms of device time
+# DRAM bytes one launch of the decode kernel moved in an ncu capture of this workload's kernel at this shape
+# (dram__bytes_read.sum + dram__bytes_write.sum); reported as roofline.traffic for that shape on one GPU only.
+NCU_DRAM_BYTES_PER_LAUNCH = 25442048
+NCU_TRAFFIC_SOURCE = "ncu capture summarised in profiles/qmv_pipe_b4g64_m1.md (not measured in this run)"
 METRIC = "decode_qmv_hbm_gbs"
 UNIT = "GB/s"
 
@@ -44,10 +51,14 @@ def alg_bytes(O, K, bits, gs, M, s_size=2, x_size=2, y_size=4):
     return O * K * bits // 8 + 2 * O * (K // gs) * s_size + M * K * x_size + M * O * y_size
 
 
-def workload_name(layers):
-    per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1)
-    return (f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1, fp16 x, fp32 y; "
-            f"{layers} distinct weight sets per step ({layers * per_launch / 1e6:.0f} MB > L2)")
+def load_synth():
+    """The synthetic-layer generators, loaded from their file so that the CPU arm does not import the product
+    package (whose import loads the CUDA library)."""
+    spec = importlib.util.spec_from_file_location("mlxq_synth", os.path.join(ROOT, "mlx-runner_b200", "synth.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["mlxq_synth"] = mod
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def measured_peaks():
@@ -57,6 +68,36 @@ def measured_peaks():
         return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained":
                 d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---- the workloads: name, per-call shapes, what both arms put into `config` ------------------------------------
+C4_PROJ = [("q|k|v", 6144, 4096), ("o", 4096, 4096), ("gate|up", 24576, 4096), ("down", 4096, 12288)]
+C4_LAYERS = 36
+C5_ROWS, C5_K = 151936, 4096
+
+
+def workload(args):
+    """Description shared by both arms: config dict, algorithmic bytes of one step on the whole job."""
+    if args.config == "c5":
+        per_call = alg_bytes(C5_ROWS, C5_K, args.bits, 64, args.batch)
+        calls = args.calls or 48
+        return {"workload": f"vocabulary head {C5_ROWS}x{C5_K} b{args.bits} g64, batch {args.batch}, fp16 x, fp32 logits; "
+                            f"{calls} calls per step ({per_call / 1e6:.0f} MB per call > L2)",
+                "rows": C5_ROWS, "in_dim": C5_K, "bits": args.bits, "group_size": 64, "batch": args.batch,
+                "launches_per_step": calls, "l2": "inputs larger than L2"}, per_call * calls
+    if args.config == "c4":
+        per_walk = C4_LAYERS * sum(alg_bytes(o, k, 4, 64, args.batch) for _, o, k in C4_PROJ)
+        walks = args.calls or 4
+        return {"workload": f"projection walk of a {C4_LAYERS}-layer transformer (hidden 4096, q|k|v 6144, gate|up 24576, down from 12288), "
+                            f"b4 g64, batch {args.batch}, fp16 x, fp32 y; {walks} walks per step ({per_walk / 1e9:.2f} GB per walk > L2)",
+                "layers": C4_LAYERS, "bits": 4, "group_size": 64, "batch": args.batch,
+                "launches_per_step": walks * C4_LAYERS * len(C4_PROJ), "l2": "inputs larger than L2"}, per_walk * walks
+    per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1)
+    launches = args.layers * args.passes
+    return {"workload": f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1, fp16 x, fp32 y; {args.passes} passes over "
+                        f"{args.layers} distinct weight sets per step ({args.layers * per_launch / 1e6:.0f} MB > L2)",
+            "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS, "group_size": GS, "batch": 1,
+            "launches_per_step": launches, "l2": "inputs larger than L2"}, per_launch * launches
 
 
 class ClockSampler:
@@ -114,31 +155,411 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_sample(seconds_target: float = 12.0):
-    """The oracle's restatement of the reference's CPU path (unpack + fp32 dequant + fp32 dot, OpenMP over
-    output rows) timed on the host cores, on one 11008 x 4096 layer of the same workload."""
-    from oracle import oracle
-    synth = importlib.import_module("mlx-runner_b200.synth")
+# ---- CPU arm ----------------------------------------------------------------------------------------------------
+def cpu_layer(args, synth):
+    """(layer, activations, note) of the CPU sample: one layer of the workload."""
+    if args.config == "c5":
+        lay = synth.make_layer_fast(C5_ROWS, C5_K, args.bits, 64, synth.F16, seed=0)
+        _, x = synth.make_activations(args.batch, C5_K, synth.F16, seed=1)
+        return [(lay, x, C5_K)], f"one {C5_ROWS}x{C5_K} {args.bits}-bit g64 head call, batch {args.batch}"
+    if args.config == "c4":
+        out = []
+        for i, (_, o, k) in enumerate(C4_PROJ):
+            lay = synth.make_layer_fast(o, k, 4, 64, synth.F16, seed=i)
+            _, x = synth.make_activations(args.batch, k, synth.F16, seed=10 + i)
+            out.append((lay, x, k))
+        return out, f"the four projections of one layer of the walk, batch {args.batch}"
     lay = synth.make_layer(O_ROWS, K_COLS, BITS, GS, synth.F16, seed=0, keep_codes=False)
     _, x = synth.make_activations(1, K_COLS, synth.F16, seed=1)
+    return [(lay, x, K_COLS)], f"one {O_ROWS}x{K_COLS} 4-bit g64 layer, M=1"
+
+
+def cpu_call(oracle, items, cores, double=False):
+    for lay, x, K in items:
+        oracle.qmatmul(lay.packed.view(np.uint8), lay.scales_raw, lay.biases_raw, lay.scale_dtype, x, K, lay.bits, lay.gs,
+                       accumulate_double=double, threads=cores)
+
+
+def cpu_bytes(items):
+    return sum(alg_bytes(l.packed.shape[0], K, l.bits, l.gs, x.shape[0]) for l, x, K in items)
+
+
+def cpu_sample(args, seconds_target: float = 12.0):
+    """The oracle's restatement of the reference's CPU path (unpack + fp32 dequant + fp32 dot, OpenMP over
+    output rows) timed on the host cores on one layer of the workload; beside it the same with a double
+    accumulator (the reference's test oracle) and the reference's other CPU route, dequantise to fp32 then BLAS."""
+    from oracle import oracle
+    synth = load_synth()
+    items, what = cpu_layer(args, synth)
     cores = len(os.sched_getaffinity(0))
-    packed8 = lay.packed.view(np.uint8)
-    call = lambda: oracle.qmatmul(packed8, lay.scales_raw, lay.biases_raw, lay.scale_dtype, x, K_COLS, BITS, GS,
-                                  accumulate_double=False, threads=cores)
-    call()
-    t0 = time.perf_counter()
-    call()
-    one = time.perf_counter() - t0
-    reps = max(3, min(200, int(seconds_target / max(one, 1e-4))))
-    best = one
-    for _ in range(reps):
+    nbytes = cpu_bytes(items)
+
+    def best_of(fn, budget):
+        fn()
         t0 = time.perf_counter()
-        call()
-        best = min(best, time.perf_counter() - t0)
-    gbs = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1) / best / 1e9
-    return {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"one {O_ROWS}x{K_COLS} 4-bit g64 layer, M=1, best of {reps + 1} calls, fp32 accumulate",
-            "ms_per_call": best * 1e3}
+        fn()
+        one = time.perf_counter() - t0
+        reps = max(2, min(200, int(budget / max(one, 1e-4))))
+        best = one
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t0)
+        return best, reps + 1
+
+    best, reps = best_of(lambda: cpu_call(oracle, items, cores), seconds_target * 0.6)
+    best_d, _ = best_of(lambda: cpu_call(oracle, items, cores, double=True), seconds_target * 0.2)
+    out = {"value": nbytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+           "sample": f"{what}, best of {reps} calls, fp32 accumulate, OpenMP over rows", "ms_per_call": best * 1e3,
+           "double_accumulate_gbs": nbytes / best_d / 1e9}
+    try:        # dequantise-then-BLAS (SieveImport.swift:90-112, 346): the dense fp32 matrix is built once, the product timed
+        lay, x, K = items[0]
+        dense = oracle.dequantize(lay.packed[:4096], lay.scales_raw[:4096], lay.biases_raw[:4096], lay.scale_dtype, K, lay.bits, lay.gs)
+        xt = np.ascontiguousarray(x.T)
+        b2, _ = best_of(lambda: dense @ xt, seconds_target * 0.1)
+        out["numpy_blas_dense_gbs"] = dense.nbytes / b2 / 1e9
+        out["numpy_blas_note"] = "x @ W_deq.T on 4096 dequantised fp32 rows (dense bytes / time; the dequantisation itself is not timed)"
+    except Exception as e:      # noqa: BLE001
+        out["numpy_blas_note"] = f"unavailable: {type(e).__name__}"
+    return out
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU algorithm (oracle port; the Swift sources cannot be built on
+    Linux) on all host cores.  A step is one layer of the workload (a bounded sample of the GPU arm's step)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    synth = load_synth()
+    cfg, _ = workload(args)
+    items, what = cpu_layer(args, synth)
+    cores = len(os.sched_getaffinity(0))
+    for _ in range(max(args.warmup, 1)):
+        cpu_call(oracle, items, cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_call(oracle, items, cores)
+    dt = time.perf_counter() - t0
+    gbs = args.steps * cpu_bytes(items) / dt / 1e9
+    sample = f"each CPU step is {what} (a bounded sample of the GPU arm's step), fp32 accumulate, OpenMP over rows"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak" if args.config == "default" else "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg, "sample": sample,
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+# ---- GPU arm ----------------------------------------------------------------------------------------------------
+def prefill_probe(mlxq, torch, device, peaks, quick=False):
+    """The prefill dequant-GEMM beside the headline: 14336 x 4096 and 4096 x 14336, 4-bit g64, bf16 in / bf16 out,
+    M = 128, 512, 2048, 8192; the pre-pass that rewrites the activations is inside the timed call."""
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    rows = []
+    try:
+        for (O, K) in ((14336, 4096), (4096, 14336)):
+            lay = synth.make_layer(O, K, 4, 64, synth.BF16, seed=3, keep_codes=False)
+            w = torch.from_numpy(lay.packed.view(np.int32)).to(device)
+            s = torch.from_numpy(lay.scales_raw.view(np.int16)).to(device).view(torch.bfloat16)
+            b = torch.from_numpy(lay.biases_raw.view(np.int16)).to(device).view(torch.bfloat16)
+            lin = mlxq.Linear(w, s, b, None, inDim=K, name="prefill")
+            for M in ((2048,) if quick else (128, 512, 2048, 8192)):
+                if lin.kernelFor(M, mlxq.BF16, mlxq.BF16) != "qgemm":
+                    rows.append({"shape": f"{O}x{K}", "M": M, "available": False})
+                    continue
+                x = torch.randn((M, K), device=device, dtype=torch.bfloat16)
+                ys = [torch.empty((M, O), device=device, dtype=torch.bfloat16) for _ in range(2)]
+                for i in range(3):
+                    lin.encode(None, x, K, ys[i % 2], O, M)
+                torch.cuda.synchronize()
+                reps = 10 if M <= 2048 else 5
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(reps):
+                    lin.encode(None, x, K, ys[i % 2], O, M)
+                e1.record()
+                torch.cuda.synchronize()
+                mlxq.streamStatus(None, device.index or 0)
+                ms = e0.elapsed_time(e1) / reps
+                tf = 2.0 * M * O * K / (ms * 1e-3) / 1e12
+                rows.append({"shape": f"{O}x{K}", "M": M, "tflops": tf, "ms": ms, "frac_of_burst_peak": tf / peaks["bf16_tflops"],
+                             "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"]})
+            del lin, w, s, b
+        head = next((r for r in rows if r["shape"] == "14336x4096" and r["M"] == 2048 and "tflops" in r), None)
+        out = {"available": head is not None, "workload": "prefill GEMM b4 g64 bf16 in/out, 14336x4096 and 4096x14336", "cases": rows}
+        if head:
+            out.update({"tflops": head["tflops"], "ms": head["ms"], "frac_of_burst_peak": head["frac_of_burst_peak"],
+                        "frac_of_sustained_peak": head["frac_of_sustained_peak"], "headline_case": "14336x4096 M=2048"})
+        return out
+    except Exception as e:      # the probe must never take the headline down
+        return {"available": False, "error": str(e)[:200], "cases": rows}
+
+
+def device_layer(torch, device, O, K, bits, gs, seed):
+    """A synthetic layer drawn on the device (uniform packed bits = uniform codes; scales and biases as the CPU
+    generator draws them) for the layers that are too large to build on the host in reasonable time."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = torch.randint(-(1 << 31), (1 << 31) - 1, (O, K * bits // 32), dtype=torch.int32, device=device, generator=g)
+    s32 = torch.randn((O, K // gs), device=device, generator=g).abs() * 0.002 + 1e-4
+    s = s32.to(torch.float16)
+    b = (-(1 << (bits - 1)) * s.float()).to(torch.float16)
+    return w, s, b
+
+
+def oracle_rows(torch, w, s, b, rows, x_np, K, bits, gs):
+    """The oracle's outputs for a few rows of a device-resident layer."""
+    from oracle import oracle
+    idx = torch.as_tensor(rows, device=w.device)
+    wp = w[idx].cpu().numpy().view(np.uint32)
+    sp = s[idx].cpu().view(torch.int16).numpy().view(np.uint16)
+    bp = b[idx].cpu().view(torch.int16).numpy().view(np.uint16)
+    return oracle.qmatmul(wp, sp, bp, 1, x_np, K, bits, gs)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    mlxq = importlib.import_module("mlx-runner_b200")
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    comm = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="nccl", device_id=device)
+        idt = torch.zeros(128, dtype=torch.uint8, device=device)
+        if rank == 0:
+            idt.copy_(torch.tensor(list(mlxq.Comm.uniqueId()), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        comm = mlxq.Comm(rank, world, local, bytes(idt.cpu().tolist()))
+    peaks = measured_peaks()
+    cfg, step_bytes = workload(args)
+    fused = comm is not None and args.gather == "fused"
+    strong = args.config != "default"
+    batch = args.batch if strong else 1
+
+    # ---- the step's calls: (layer, activations, rows of the whole layer) in order ---------------------------------
+    calls, keep = [], []
+    if args.config == "default":
+        for i in range(args.layers):
+            lay = synth.make_layer(O_ROWS, K_COLS, BITS, GS, synth.F16, seed=1000 * rank + i, keep_codes=False)
+            w = torch.from_numpy(lay.packed.view(np.int32)).to(device)
+            s = torch.from_numpy(lay.scales_raw.view(np.int16)).to(device).view(torch.float16)
+            b = torch.from_numpy(lay.biases_raw.view(np.int16)).to(device).view(torch.float16)
+            keep.append((w, s, b))
+            if world > 1:
+                lin = mlxq.Linear.shard(w, s, b, None, inDim=K_COLS, rank=rank, nranks=world, full=False, name=f"layer{i}", device=local)
+            else:
+                lin = mlxq.Linear(w, s, b, None, inDim=K_COLS, name=f"layer{i}", device=local)
+            calls.append((lin, K_COLS, O_ROWS * world))
+        calls = calls * args.passes
+    else:
+        shapes = [(C5_ROWS, C5_K, args.bits)] if args.config == "c5" else [(o, k, 4) for _ in range(C4_LAYERS) for _, o, k in C4_PROJ]
+        distinct = {}
+        for i, (O, K, bits) in enumerate(shapes):
+            # every rank draws the whole layer's rows it owns: the same seed gives the same full layer on every rank
+            rows = O // world
+            w, s, b = device_layer(torch, device, O, K, bits, 64, seed=7 + i)
+            r0 = rank * rows
+            w, s, b = w[r0:r0 + rows].contiguous(), s[r0:r0 + rows].contiguous(), b[r0:r0 + rows].contiguous()
+            keep.append((w, s, b))
+            if world > 1:
+                lin = mlxq.Linear.shard(w, s, b, None, inDim=K, rank=rank, nranks=world, full=False, name=f"call{i}", device=local)
+            else:
+                lin = mlxq.Linear(w, s, b, None, inDim=K, name=f"call{i}", device=local)
+            distinct[i] = (lin, K, O)
+        n_rep = args.calls or (48 if args.config == "c5" else 4)
+        calls = [distinct[i] for _ in range(n_rep) for i in range(len(shapes))]
+    ks = sorted({k for _, k, _ in calls})
+    x_host = {k: torch.from_numpy(synth.make_activations(batch, k, synth.F16, seed=7 + k)[0].view(np.int16)).view(torch.float16).pin_memory() for k in ks}
+    x_dev = {k: x_host[k].to(device) for k in ks}
+    max_rows = max(o for _, _, o in calls)
+    last = calls[-1]
+    y_dev = torch.zeros((batch, max_rows), dtype=torch.float32, device=device)          # non-fused paths write here
+    y_keep = torch.zeros((batch, last[2]), dtype=torch.float32, device=device)          # the step's result (last call)
+    y_host = torch.empty((batch, last[2]), dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream()
+    if fused:
+        comm.window(((batch * max_rows * 4 + 255) // 256) * 256)      # collective: the peer-mapped gather windows
+
+    def step(keep_output=False, gather=True):
+        st = torch.cuda.current_stream()        # the capture stream while the step is being recorded into a graph
+        out = None
+        for lin, K, total in calls:
+            if comm is not None and gather:
+                if fused:
+                    # the decode kernel stores its rows into every rank's window itself; no collective kernel
+                    # (each call waits for the peers' rows of the one before it, the explicit wait covers the last)
+                    out = comm.forwardGatherFused(lin, st, x_dev[K], K, batch, wait=False)
+                else:
+                    comm.forwardGather(lin, st, x_dev[K], K, y_dev, total, batch)
+                    out = y_dev[:, :total]
+            else:
+                lin.encode(st, x_dev[K], K, y_dev[:, lin.rowOffset:], max_rows, batch)
+                out = y_dev[:, :total]
+        if fused and gather:
+            comm.wait(st)
+        if keep_output:
+            y_keep.copy_(out[:, :last[2]], non_blocking=True)
+
+    def step_e2e():
+        for k in ks:
+            x_dev[k].copy_(x_host[k], non_blocking=True)
+        step(keep_output=True)
+        y_host.copy_(y_keep, non_blocking=True)
+        stream.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    # One GPU: the step's launches are recorded once into a CUDA graph and replayed, so that the figure is the
+    # kernels' and not the Python loop's (per-call host cost is 5-15 us here, a launch takes ~8 us).  The same
+    # step with one API call per launch is timed beside it ("api_calls"), which is the mode sharded runs use:
+    # every fused-gather call carries a fresh epoch as a kernel argument and is not captured.
+    timed_step, launch_mode = step, "one API call per launch"
+    if world == 1 and not args.no_graph:
+        try:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            mlxq.streamStatus(stream, local)
+            timed_step, launch_mode = graph.replay, "CUDA graph of the step's launches, replayed"
+        except Exception as e:  # noqa: BLE001
+            launch_mode = f"one API call per launch (graph capture failed: {type(e).__name__})"
+    windows = []
+    t_a = time.perf_counter()
+    ms = timed(timed_step, args.steps)
+    windows.append((t_a, time.perf_counter()))
+    ms_api = timed(step, max(3, args.steps // 4)) / max(3, args.steps // 4) if timed_step is not step else ms / args.steps
+    ms_kernel_only = None
+    if world > 1:
+        n = max(3, args.steps // 4)
+        ms_kernel_only = timed(lambda: step(gather=False), n) / n
+    for _ in range(2):
+        step_e2e()
+    t_a = time.perf_counter()
+    ms_e2e = timed(step_e2e, args.steps)
+    windows.append((t_a, time.perf_counter()))
+    clocks = sampler.stop(windows) if rank == 0 else None
+    mlxq.streamStatus(stream, local)
+
+    # ---- correctness of what was timed: the last call's output on this rank against the oracle, a sample of rows ----
+    lin, K, total = last
+    step(keep_output=True)
+    torch.cuda.synchronize()
+    got = y_keep.cpu().numpy()
+    check = "ok"
+    try:
+        from oracle import oracle
+        g = np.random.default_rng(rank)
+        if args.config == "default":
+            w, s, b = keep[(len(calls) - 1) % args.layers]
+            bits_l, rows_l = BITS, O_ROWS
+        else:
+            w, s, b = keep[-1]
+            bits_l, rows_l = lin.bits, w.shape[0]
+        sample = np.sort(g.choice(rows_l, size=64, replace=False))
+        xv = x_host[K].float().numpy()
+        ref = oracle_rows(torch, w, s, b, sample, xv, K, bits_l, 64)
+        err = oracle.max_rel_err(got[:, lin.rowOffset + sample], ref)
+        ok = err < 1e-3
+        if world > 1:
+            # the rows the other ranks computed: compare with what they hold
+            mine = torch.from_numpy(got).to(device)
+            ref_all = mine.clone()
+            dist.broadcast(ref_all, 0)
+            same = bool(torch.equal(mine, ref_all)) if fused or args.gather == "nccl" else True
+            flag = torch.tensor([1 if (ok and same) else 0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(flag.item())
+        if not ok:
+            check = f"FAILED (max relative error {err:.3g} on rank {rank})"
+    except Exception as e:      # noqa: BLE001
+        check = f"not run: {type(e).__name__}: {str(e)[:80]}"
+
+    launches = args.steps * len(calls)
+    scale = world if args.config == "default" else 1          # weak scaling: every rank does a full step's bytes
+    value = scale * args.steps * step_bytes / (ms * 1e-3) / 1e9
+    e2e_value = scale * args.steps * step_bytes / (ms_e2e * 1e-3) / 1e9
+    # Roofline of the dominant kernel (the matvec): this rank's algorithmic bytes of a step over the step's time
+    # (at N > 1 that time includes the gather, so the N = 1 line is the kernel's figure).
+    per_rank_bytes = step_bytes / (1 if args.config == "default" else world)
+    achieved = per_rank_bytes * args.steps / (ms * 1e-3) / 1e9
+    if rank == 0:
+        probe = prefill_probe(mlxq, torch, device, peaks) if world == 1 and not args.no_prefill and args.config == "default" else {"available": False}
+        cpu = cpu_sample(args, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
+        cfg = dict(cfg)
+        cfg["launch"] = launch_mode
+        cfg["parallelism"] = (f"row-shard x{world} + " + ("peer-store gather fused into the kernel" if fused else "ncclAllGather")) if world > 1 else "single GPU"
+        captured_shape = args.config == "default" and world == 1 and args.layers == LAYERS
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": cfg,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(sum(x_host[k].numel() for k in ks) * 2),
+                    "d2h_bytes_per_step": int(y_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH if captured_shape else None,
+                         "traffic_source": NCU_TRAFFIC_SOURCE if captured_shape else None, "peak_source": peaks["source"],
+                         "frac_of_nominal_8000": achieved / 8000.0, "bytes_per_step_per_gpu": per_rank_bytes},
+            "api_calls": {"ms_per_step": ms_api, "value": scale * step_bytes / (ms_api * 1e-3) / 1e9,
+                          "note": "the same step with one API call per launch (the mode of sharded runs)"},
+            "output_check": check,
+            "prefill": probe,
+        }
+        if world > 1:
+            out["gather_check"] = check
+            out["split"] = {"kernel_ms_per_step": ms_kernel_only, "gather_ms_per_step": ms / args.steps - ms_kernel_only,
+                            "note": "the step without its gathers (shard matvecs only), then the difference"}
+        if cpu:
+            out["cpu_baseline"] = cpu
+        print(json.dumps(out), flush=True)
+        if check.startswith("FAILED"):
+            raise SystemExit(f"bench.py: {check}")
+    if comm is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
 
 
 def run_sweep(args):
@@ -149,6 +570,7 @@ def run_sweep(args):
     mlxq = importlib.import_module("mlx-runner_b200")
     synth = importlib.import_module("mlx-runner_b200.synth")
     dev = torch.device("cuda", 0)
+    peak = measured_peaks()["hbm_gbs"]
 
     def one(O, K, bits, gs, M, L=8, reps=10):
         layers, keep = [], []
@@ -185,265 +607,35 @@ def run_sweep(args):
         us = e0.elapsed_time(e1) * 1e3 / (reps * L)
         return us, alg_bytes(O, K, bits, gs, M) / us / 1e3
 
-    print("| shape (out x in) | bits | group | M | us per launch | GB/s |")
-    print("|---|---|---|---|---|---|")
+    print("| shape (out x in) | bits | group | M | us per launch | GB/s | of measured peak |")
+    print("|---|---|---|---|---|---|---|")
     cases = [(11008, 4096, b, 64, m) for b in (2, 3, 4, 5, 6, 8) for m in (1, 8)]
     cases += [(4096, 11008, 4, 64, m) for m in (1, 8)] + [(11008, 4096, 4, gs, m) for gs in (32, 128) for m in (1, 4)]
+    cases += [(24576, 4096, 4, 64, 1), (6144, 4096, 4, 64, 1), (4096, 12288, 4, 64, 1), (4096, 4096, 4, 64, 1)]
     for O, K, bits, gs, M in cases:
         us, gbs = one(O, K, bits, gs, M)
-        print(f"| {O} x {K} | {bits} | {gs} | {M} | {us:.1f} | {gbs:.0f} |", flush=True)
-
-
-def run_reference(args):
-    """--impl reference: the reference's CPU algorithm (oracle port; the Swift sources cannot be built on
-    Linux) on all host cores.  A step is one matvec over one layer of the workload."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    from oracle import oracle
-    synth = importlib.import_module("mlx-runner_b200.synth")
-    lay = synth.make_layer(O_ROWS, K_COLS, BITS, GS, synth.F16, seed=0, keep_codes=False)
-    _, x = synth.make_activations(1, K_COLS, synth.F16, seed=1)
-    cores = len(os.sched_getaffinity(0))
-    packed8 = lay.packed.view(np.uint8)
-    call = lambda: oracle.qmatmul(packed8, lay.scales_raw, lay.biases_raw, lay.scale_dtype, x, K_COLS, BITS, GS,
-                                  accumulate_double=False, threads=cores)
-    for _ in range(max(args.warmup, 1)):
-        call()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        call()
-    dt = time.perf_counter() - t0
-    gbs = args.steps * alg_bytes(O_ROWS, K_COLS, BITS, GS, 1) / dt / 1e9
-    sample = f"one {O_ROWS}x{K_COLS} 4-bit g64 layer per step, M=1, fp32 accumulate, OpenMP over rows"
-    print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(LAYERS), "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS,
-                   "group_size": GS, "batch": 1, "launches_per_step": 1,
-                   "sample": "each CPU step is one of the workload's weight sets (a step of the GPU arm is 16 of them)"},
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
-
-
-def prefill_probe(mlxq, torch, device, peaks):
-    """The prefill dequant-GEMM beside the headline: 14336 x 4096, 4-bit g64, bf16 in/out, M = 2048."""
-    synth = importlib.import_module("mlx-runner_b200.synth")
-    O, K, M = 14336, 4096, 2048
-    try:
-        lay = synth.make_layer(O, K, 4, 64, synth.BF16, seed=3, keep_codes=False)
-        w = torch.from_numpy(lay.packed.view(np.int32)).to(device)
-        s = torch.from_numpy(lay.scales_raw.view(np.int16)).to(device).view(torch.bfloat16)
-        b = torch.from_numpy(lay.biases_raw.view(np.int16)).to(device).view(torch.bfloat16)
-        lin = mlxq.Linear(w, s, b, None, inDim=K, name="prefill")
-        if lin.kernelFor(M, mlxq.BF16, mlxq.BF16) != "qgemm":
-            return {"available": False}
-        x = torch.randn((M, K), device=device, dtype=torch.bfloat16)
-        ys = [torch.empty((M, O), device=device, dtype=torch.bfloat16) for _ in range(2)]
-        for i in range(3):
-            lin.encode(None, x, K, ys[i % 2], O, M)
-        torch.cuda.synchronize()
-        reps = 10
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(reps):
-            lin.encode(None, x, K, ys[i % 2], O, M)
-        e1.record()
-        torch.cuda.synchronize()
-        mlxq.streamStatus(None, device.index or 0)
-        ms = e0.elapsed_time(e1) / reps
-        tf = 2.0 * M * O * K / (ms * 1e-3) / 1e12
-        return {"available": True, "workload": f"prefill GEMM {O}x{K} b4 g64 M={M} bf16", "tflops": tf, "ms": ms,
-                "frac_of_burst_peak": tf / peaks["bf16_tflops"], "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"]}
-    except Exception as e:      # the probe must never take the headline down
-        return {"available": False, "error": str(e)[:200]}
-
-
-def run_ours(args):
-    LAYERS = args.layers
-    import torch
-    import torch.distributed as dist
-    mlxq = importlib.import_module("mlx-runner_b200")
-    synth = importlib.import_module("mlx-runner_b200.synth")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path")
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    comm = None
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group(backend="nccl", device_id=device)
-        idt = torch.zeros(128, dtype=torch.uint8, device=device)
-        if rank == 0:
-            idt.copy_(torch.tensor(list(mlxq.Comm.uniqueId()), dtype=torch.uint8))
-        dist.broadcast(idt, 0)
-        comm = mlxq.Comm(rank, world, local, bytes(idt.cpu().tolist()))
-    peaks = measured_peaks()
-
-    # LAYERS distinct weight sets on this rank (its shard of each layer when world > 1).
-    layers, keep = [], []
-    for i in range(LAYERS):
-        lay = synth.make_layer(O_ROWS, K_COLS, BITS, GS, synth.F16, seed=1000 * rank + i, keep_codes=False)
-        w = torch.from_numpy(lay.packed.view(np.int32)).to(device)
-        s = torch.from_numpy(lay.scales_raw.view(np.int16)).to(device).view(torch.float16)
-        b = torch.from_numpy(lay.biases_raw.view(np.int16)).to(device).view(torch.float16)
-        keep.append((w, s, b))
-        if world > 1:
-            layers.append(mlxq.Linear.shard(w, s, b, None, inDim=K_COLS, rank=rank, nranks=world, full=False,
-                                            name=f"layer{i}", device=local))
-        else:
-            layers.append(mlxq.Linear(w, s, b, None, inDim=K_COLS, name=f"layer{i}", device=local))
-    total_rows = O_ROWS * world
-    x_raw, _ = synth.make_activations(1, K_COLS, synth.F16, seed=7)
-    x_host = torch.from_numpy(x_raw.view(np.int16)).view(torch.float16).pin_memory()
-    x_dev = x_host.to(device)
-    y_dev = torch.zeros((LAYERS, total_rows), dtype=torch.float32, device=device)
-    y_host = torch.empty((LAYERS, total_rows), dtype=torch.float32).pin_memory()
-    stream = torch.cuda.current_stream()
-
-    fused = comm is not None and args.gather == "fused"
-    if fused:
-        comm.window(((total_rows * 4 + 255) // 256) * 256)      # collective: the peer-mapped gather windows
-
-    def step(keep_outputs=False):
-        stream = torch.cuda.current_stream()        # the capture stream while the step is being recorded into a graph
-        for i, lin in enumerate(layers):
-            if fused:
-                # the decode kernel stores its rows into every rank's window itself; no collective kernel
-                # (each call waits for the peers' rows of the one before it, the explicit wait covers the last)
-                out = comm.forwardGatherFused(lin, stream, x_dev, K_COLS, 1, wait=keep_outputs)
-                if keep_outputs:
-                    y_dev[i].copy_(out[0], non_blocking=True)
-            elif comm is not None:
-                comm.forwardGather(lin, stream, x_dev, K_COLS, y_dev[i], total_rows, 1)
-            else:
-                lin.encode(stream, x_dev, K_COLS, y_dev[i], O_ROWS, 1)
-        if fused and not keep_outputs:
-            comm.wait(stream)
-
-    def step_e2e():
-        x_dev.copy_(x_host, non_blocking=True)
-        step(keep_outputs=True)
-        y_host.copy_(y_dev, non_blocking=True)
-        stream.synchronize()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        step()
-    # One GPU: the step's launches are recorded once into a CUDA graph and replayed, so that the figure is the
-    # kernels' and not the Python loop's (per-call host cost is 5-15 us here, the kernel takes ~10 us).  The
-    # end-to-end leg below keeps calling the public API.  Sharded runs are not graphed: every fused-gather call
-    # carries a fresh epoch.
-    timed_step, launch_mode = step, "one API call per launch"
-    if world == 1 and not args.no_graph:
-        try:
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step()
-            for _ in range(3):
-                graph.replay()
-            torch.cuda.synchronize()
-            mlxq.streamStatus(stream, local)
-            timed_step, launch_mode = graph.replay, "CUDA graph of the step's launches, replayed"
-        except Exception as e:  # noqa: BLE001
-            launch_mode = f"one API call per launch (graph capture failed: {type(e).__name__})"
-    windows = []
-    t_a = time.perf_counter()
-    ms = timed(timed_step, args.steps)
-    windows.append((t_a, time.perf_counter()))
-    for _ in range(2):
-        step_e2e()
-    t_a = time.perf_counter()
-    ms_e2e = timed(step_e2e, args.steps)
-    windows.append((t_a, time.perf_counter()))
-    clocks = sampler.stop(windows) if rank == 0 else None
-    mlxq.streamStatus(stream, local)
-
-    per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1)
-    launches = args.steps * LAYERS
-    value = world * launches * per_launch / (ms * 1e-3) / 1e9
-    e2e_value = world * launches * per_launch / (ms_e2e * 1e-3) / 1e9
-    # Roofline of the dominant kernel (the matvec): per-launch algorithmic bytes over the mean launch time
-    # of the timed region (at N > 1 that time includes the gather, so the N = 1 line is the kernel's figure).
-    achieved = per_launch / (ms * 1e-3 / launches) / 1e9
-    out = None
-    if rank == 0:
-        probe = prefill_probe(mlxq, torch, device, peaks) if world == 1 and not args.no_prefill else {"available": False}
-        cpu = cpu_sample(args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
-        out = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(LAYERS),
-                       "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS, "group_size": GS, "batch": 1,
-                       "launches_per_step": LAYERS, "l2": "inputs larger than L2", "launch": launch_mode,
-                       "parallelism": (f"row-shard x{world} + " + ("peer-store gather fused into the kernel" if fused else
-                                                                   "ncclAllGather")) if world > 1 else "single GPU"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel() * 2),
-                    "d2h_bytes_per_step": int(y_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                         "frac_of_nominal_8000": achieved / 8000.0, "bytes_per_launch": per_launch},
-            "prefill": probe,
-        }
-        if cpu:
-            out["cpu_baseline"] = cpu
-        # DRAM bytes one launch of the decode kernel moved under ncu (dram__bytes_read.sum + dram__bytes_write.sum,
-        # from the capture summarised under profiles/); the capture is of this workload's kernel at this shape.
-        out["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH      # every rank runs this shape (weak scaling)
-        print(json.dumps(out), flush=True)
-    if comm is not None:
-        torch.cuda.synchronize()
-        dist.barrier()
-        comm.close()
-        dist.destroy_process_group()
+        print(f"| {O} x {K} | {bits} | {gs} | {M} | {us:.1f} | {gbs:.0f} | {gbs / peak:.2f} |", flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="default", choices=["default", "c4", "c5"],
+                    help="default: the 11008x4096 sweep shape (weak scaling); c4: projection walk; c5: vocabulary head (strong scaling)")
+    ap.add_argument("--bits", type=int, default=8, choices=[6, 8], help="c5: bit width of the head")
+    ap.add_argument("--batch", type=int, default=1, help="c4 / c5: tokens per call")
+    ap.add_argument("--calls", type=int, default=0, help="c4: walks per step, c5: calls per step (0 = default)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length (0 = skip)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM probe")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: rows stored into the peers' windows by the decode kernel (fused) or ncclAllGather after it")
     ap.add_argument("--sweep", action="store_true", help="print the decode sweep table (bits x group x M) instead of the JSON line")
     ap.add_argument("--no-graph", action="store_true", help="time plain API calls instead of a replayed CUDA graph")
-    ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight sets per step (default 16)")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight sets per pass (default 16)")
+    ap.add_argument("--passes", type=int, default=PASSES, help="passes over the weight sets per step (default 40)")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)

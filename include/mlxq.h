@@ -213,7 +213,9 @@ MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_str
  * ranks: the rows are complete in `stream` order once the next fused call of the communicator has begun
  * (it waits for the peers before it reads its activations, while its weight copies are already in flight)
  * or after mlxq_comm_wait(c, stream), which enqueues that wait alone; any other reader needs the latter.
- * The address stays valid until the second-next fused call (calls alternate between the two buffers).
+ * The rows may be read by work enqueued on `stream` before this rank's NEXT fused call on the communicator, and only
+ * by such work: calls alternate between two buffers, and a peer that runs ahead starts storing its second-next
+ * call's rows into this buffer as soon as this rank has published its next call.
  * Every rank must issue the same sequence of fused calls.  Only shapes the persistent decode kernel serves
  * (T <= 16, the usual alignment) are accepted; others return MLXQ_UNSUPPORTED and leave the communicator
  * untouched -- use mlxq_linear_forward_gather for those.  A wait for a peer gives up after two seconds:

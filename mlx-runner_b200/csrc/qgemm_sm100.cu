@@ -45,14 +45,6 @@
 
 namespace mlxq {
 
-#ifdef MLXQ_TRACE
-// Timeline probe for development builds.
-__device__ unsigned long long g_gemm_trace[148 * 256];
-#define GTRACE(slot) do { if ((slot) < 256) g_gemm_trace[blockIdx.x * 256 + (slot)] = global_ns(); } while (0)
-#else
-#define GTRACE(slot) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int BM = 256;                 // weight rows per CTA tile (two M=128 MMA tiles)
@@ -74,14 +66,6 @@ constexpr int MMA_WARP = 1;             // issuer of half 0; it also owns the te
 constexpr int MMA_WARP2 = 3;            // issuer of half 1
 constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16;
 constexpr int TMEM_COLS = 512;
-// (timing aid, see MLXQ_GEMM_ABLATE)
-__host__ __device__ constexpr bool ablate_mma() {
-#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 16)
-    return true;
-#else
-    return false;
-#endif
-}
 constexpr uint32_t SCALE_MARKER = 0x7E00u;   // fp16 NaN in a staged entry: scale * 2^20 does not fit fp16
 constexpr int D_COL0 = 0;               // two fp32 accumulators of BN columns each
 constexpr int A_COL0 = 2 * BN;          // A ring: S_A stages x 2 halves x 32 columns
@@ -178,7 +162,6 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     if (it >= S_X && !mbar_wait(&bars->empty_x[s], ((it / S_X) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     mbar_expect_tx(&bars->full_x[s], X_STAGE);
                     tma_load_2d(x_tiles + s * X_STAGE, &map_x, &bars->full_x[s], ks * BK, tok0);
-                    if (it < 24) GTRACE(160 + it);
                 }
             }
             // Before leaving, see every copy this thread issued land (bounded), so that no bulk copy is in
@@ -201,7 +184,6 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     const int sw = wi % S_W;
                     if (wi >= S_W && !mbar_wait(&bars->empty_w[sw], ((wi / S_W) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     mbar_expect_tx(&bars->full_w[sw], W_SLAB);
-                    if (wi < 12) GTRACE(184 + wi);
                     tma_load_2d(w_slabs + sw * W_SLAB, &map_w, &bars->full_w[sw], ks * (BK / 2), row0);
                 }
             }
@@ -224,18 +206,16 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     if (!mbar_wait(&bars->full_x[s], (it / S_X) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     if (!mbar_wait(&bars->full_a[sa], (it / S_A) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
                     tc_fence_after();
-                    if (warp == MMA_WARP && tile_i == 0 && ks < 24) GTRACE(ks * 2);
                     const uint64_t bdesc = smem_desc_sw128(smem_u32(x_tiles + s * X_STAGE));
                     {
                         const int half = warp == MMA_WARP ? 0 : 1;
                         const uint32_t d_addr = tmem + D_COL0 + half * BN;
 #pragma unroll
-                        for (int kk = 0; kk < (ablate_mma() ? 0 : BK / 16); kk++)
+                        for (int kk = 0; kk < BK / 16; kk++)
                             tc_mma_ts(d_addr, tmem + a_col(sa, half, kk >> 1) + (kk & 1) * 8, bdesc + static_cast<uint64_t>(kk * 2), a.idesc, (ks | kk) != 0);
                     }
                     tc_commit(&bars->empty_x[s]);      // the activation tile of stage s is free again
                     tc_commit(&bars->empty_a[sa]);     // so is the A stage in tensor memory
-                    if (warp == MMA_WARP && tile_i == 0 && ks < 24) GTRACE(ks * 2 + 1);
                 }
                 if (ok) tc_commit(&bars->d_full);      // accumulators of this tile are complete
             }
@@ -315,9 +295,6 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const uint4* ptab = a.pairs + static_cast<size_t>(khalf) * a.o_pad + (m_tile * BM + half * 128 + r);
             uint32_t p_nxt[4], p_cur[4] = {0u, 0u, 0u, 0u};
             auto fetch_slab = [&](int slab) {
-#ifdef MLXQ_GEMM_ABLATE
-                if (MLXQ_GEMM_ABLATE & 1) { p_nxt[0] = p_nxt[1] = p_nxt[2] = p_nxt[3] = 0x10103c00u + slab; return; }
-#endif
                 const uint4* e = ptab + static_cast<size_t>(slab) * 2 * a.o_pad;
                 asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(p_nxt[0]), "=r"(p_nxt[1]), "=r"(p_nxt[2]), "=r"(p_nxt[3]) : "l"(e));
             };
@@ -355,18 +332,11 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     sc_bits = *reinterpret_cast<const uint32_t*>(&s2);
                 }
                 const __half2 sc = *reinterpret_cast<const __half2*>(&sc_bits);
-                if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(208 + (wi - 1) * 2);
                 if (sub == 0 && !mbar_wait_warp(&bars->full_w[sw], ((wi - 1) / S_W) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
-                if (sub == 0 && warp == DEQ_WARP0 && lane == 0 && wi <= 12) GTRACE(209 + (wi - 1) * 2);
-                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4);
                 // row of 128 bytes, 16-byte chunk (sub*2 + khalf), stored with the 128-byte swizzle (chunk ^ row%8)
                 // (fetching the next stage's chunk a stage early was tried: slower, 660 vs 690 TFLOP/s)
                 const int wr = half * 128 + r;
-#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 4)
-                const uint4 pk = make_uint4(0x12345678u + it, 0x9abcdef0u, 0x0f1e2d3cu + lane, 0x4b5a6978u);
-#else
                 const uint4 pk = *reinterpret_cast<const uint4*>(w_slabs + sw * W_SLAB + wr * 128 + (((sub * 2 + khalf) ^ (wr & 7)) << 4));
-#endif
                 if (sub == W_SPAN - 1 || ks == k_stages - 1) {
                     // last read of the slab by this warp
                     __syncwarp();
@@ -376,12 +346,6 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 uint32_t v[16];
                 // One decision per warp and stage, outside the unrolled loops: left per lane inside them, the
                 // compiler evaluated both dequant forms for every value (3x the half-precision FMAs).
-#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 2)
-                if (true) {
-#pragma unroll
-                    for (int i = 0; i < 16; i++) v[i] = words[i & 3] + sc_bits + bi_bits;
-                } else
-#endif
                 if (__all_sync(0xffffffffu, small)) {
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
@@ -414,20 +378,12 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         }
                     }
                 }
-                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 1);
-#if !(defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 256))
                 if (it >= S_A && !mbar_wait_warp(&bars->empty_a[sa], ((it / S_A) - 1) & 1, &bars->abort_flag, a.err)) { ok = false; break; }
-#endif
-                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 2);
                 __syncwarp();                                   // the per-lane dequant branches end here
                 tc_fence_after();
-#if defined(MLXQ_GEMM_ABLATE) && (MLXQ_GEMM_ABLATE & 8)
-                if (v[0] == 0x12345u && v[7] == 0x54321u)
-#endif
                 tc_st16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + a_col(sa, half, khalf), v);
                 stored_sa = sa;
                 publish();                                      // (publishing a stage late was tried: 1 % slower)
-                if (warp == DEQ_WARP0 && lane == 0 && it < 24) GTRACE(64 + it * 4 + 3);
             }
             publish();                                          // the tile's last stage
             if (ok) pending_tile = tile;
@@ -456,10 +412,7 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 namespace wide {
 
 constexpr int BM = 128, BN = 256;
-#ifndef MLXQ_WIDE_SX
-#define MLXQ_WIDE_SX 4
-#endif
-constexpr int S_X = MLXQ_WIDE_SX;       // activation stages of 32 KB
+constexpr int S_X = 4;                  // activation stages of 32 KB
 constexpr int S_W = 3;                  // weight slabs of 16 KB (128 rows x 128 bytes = W_SPAN stages)
 constexpr int S_A = 8;                  // TMEM stages of the A operand, 32 columns each
 constexpr int X_STAGE = BN * BK * 2;    // 32768
@@ -889,10 +842,7 @@ cudaMemPool_t scratch_pool(int device) {
 }  // namespace
 
 // Batches of more than 128 tokens take the wide tile (128 rows x 256 tokens), shorter ones the tall one (256 x 128).
-static bool use_wide(long long T) {
-    static const int forced = [] { const char* e = std::getenv("MLXQ_GEMM_TILE"); return e ? (e[0] == 'w' ? 1 : e[0] == 't' ? 2 : 0) : 0; }();
-    return forced == 1 || (forced == 0 && T > 128);
-}
+static bool use_wide(long long T) { return T > 128; }
 
 int qgemm_tile_tokens(const GemmLayer& L, int x_dtype, long long x_stride, const void* x, long long T) {
     if (L.bits != 4 || L.K % BK != 0 || L.K < 2 * S_A * BK || L.gs < 32 || (L.gs & (L.gs - 1)) != 0 || L.O < 1 || T < 1) return 0;

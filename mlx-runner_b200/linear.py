@@ -401,7 +401,8 @@ class Comm:
     def forwardGatherFused(self, layer: Linear, stream, x, xStride: int, T: int, xDtype: Optional[int] = None,
                            wait: bool = True):
         """Shard matvec whose kernel stores its rows into every rank's window.  Returns the gathered output as
-        an fp32 CUDA tensor [T, total rows] that aliases the window: valid until the second-next fused call.
+        an fp32 CUDA tensor [T, total rows] that aliases the window: readable by work enqueued on ``stream`` before this
+        rank's next fused call, and only by such work (a peer that runs ahead reuses the buffer after that).
         ``wait=False`` leaves out the wait for the peers' rows: right when the next thing in the stream is
         another fused call (it waits itself) -- call ``wait(stream)`` before anything else reads the tensor."""
         out = C.c_void_p()

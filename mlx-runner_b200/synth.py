@@ -73,6 +73,17 @@ def make_layer(O: int, K: int, bits: int, gs: int, scale_dtype: int = F16, seed:
     return SynthLayer(q if keep_codes else None, packed, s_raw, b_raw, s_val, b_val, bits, gs, scale_dtype)
 
 
+def make_layer_fast(O: int, K: int, bits: int, gs: int, scale_dtype: int = F16, seed: int = 0) -> SynthLayer:
+    """The same distribution for layers too large to draw code by code (a vocabulary-sized head): uniform codes are
+    uniform bits, so the packed words are drawn directly.  ``q`` is not kept."""
+    g = np.random.default_rng(seed)
+    packed = g.integers(0, 1 << 32, size=(O, K * bits // 32), dtype=np.uint32)
+    scale = (np.abs(g.standard_normal((O, K // gs), dtype=np.float32)) * np.float32(0.002) + np.float32(1e-4))
+    s_raw, s_val = round_to(scale, scale_dtype)
+    b_raw, b_val = round_to((-np.float32(1 << (bits - 1)) * s_val).astype(np.float32), scale_dtype)
+    return SynthLayer(None, packed, s_raw, b_raw, s_val, b_val, bits, gs, scale_dtype)
+
+
 def make_activations(T: int, K: int, dtype: int = F16, seed: int = 1):
     """(raw storage array [T, K], values as fp32)."""
     g = np.random.default_rng(seed)

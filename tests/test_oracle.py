@@ -167,3 +167,32 @@ def test_oracle_reproduces_the_committed_golden_cases(oracle):
         y2 = oracle.qmatmul(c.packed, c.scales, c.biases, c.sdt, c.x, c.K, c.bits, c.gs,
                             bias=None if c.bias is None else fx.bias)
         assert oracle.max_rel_err(y2, c.y) < 1e-3, c.name
+
+
+def test_two_independent_restatements_agree(oracle):
+    # oracle/ follows the reference's Swift test code; oracle/metal_restatement.py was written from the Metal
+    # kernel text (unpack8, Kernels.swift:34-55; qmm, Kernels.swift:60-113).  Codes must agree bit for bit; outputs
+    # to fp32 summation noise (the kernel text accumulates in fp32 over 32 lanes, the Swift oracle in double):
+    # max |a - b| / max(1, |b|) < 2e-5, fifty times inside the 1e-3 bar the kernels are held to.
+    import importlib
+    import golden_cases
+    from oracle import metal_restatement as mr
+    for c in golden_cases.load():
+        rows = np.ascontiguousarray(c.packed).view(np.uint8).reshape(c.O, -1)
+        codes = mr.unpack8(rows, c.bits)
+        assert np.array_equal(codes, c.q), c.name
+        assert np.array_equal(codes, oracle.unpack(c.packed, c.K, c.bits)), c.name
+        y = mr.qmm(c.packed, c.scales, c.biases, c.sdt, c.x, c.K, c.bits, c.gs)
+        ref = oracle.qmatmul(c.packed, c.scales, c.biases, c.sdt, c.x, c.K, c.bits, c.gs)
+        assert oracle.max_rel_err(y, ref) < 2e-5, c.name
+    # the benchmark's own generators (BASELINE distributions) at full K
+    synth = importlib.import_module("mlx-runner_b200.synth")
+    for bits, gs, sdt in [(4, 64, synth.F16), (6, 64, synth.F16), (8, 64, synth.F16), (3, 32, synth.BF16), (5, 128, synth.BF16),
+                          (2, 64, synth.F16)]:
+        lay = synth.make_layer(48, 4096, bits, gs, sdt, seed=bits)
+        rows = np.ascontiguousarray(lay.packed).view(np.uint8).reshape(48, -1)
+        assert np.array_equal(mr.unpack8(rows, bits), lay.q)
+        _, x = synth.make_activations(3, 4096, synth.F16, seed=bits)
+        y = mr.qmm(lay.packed, lay.scales_raw, lay.biases_raw, sdt, x, 4096, bits, gs)
+        ref = oracle.qmatmul(lay.packed, lay.scales_raw, lay.biases_raw, sdt, x, 4096, bits, gs)
+        assert oracle.max_rel_err(y, ref) < 2e-5, (bits, gs)
