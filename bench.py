@@ -447,10 +447,11 @@ def run_ours(args):
         step()
     # One GPU: the step's launches are recorded once into a CUDA graph and replayed, so that the figure is the
     # kernels' and not the Python loop's (per-call host cost is 5-15 us here, a launch takes ~8 us).  The same
-    # step with one API call per launch is timed beside it ("api_calls"), which is the mode sharded runs use:
-    # every fused-gather call carries a fresh epoch as a kernel argument and is not captured.
+    # step with one API call per launch is timed beside it ("api_calls").  Sharded runs with the fused gather are
+    # captured the same way (the gather's call number lives on the device); the NCCL variant is not.
     timed_step, launch_mode = step, "one API call per launch"
-    if world == 1 and not args.no_graph:
+    graphable = world == 1 or (fused and len(calls) % 2 == 0)      # a replayed sequence keeps the two window buffers alternating
+    if graphable and not args.no_graph:
         try:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()

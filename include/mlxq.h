@@ -97,6 +97,12 @@ MLXQ_API int mlxq_linear_create(const mlxq_linear_desc* desc, mlxq_linear_t* out
 MLXQ_API int mlxq_linear_create_shard(const mlxq_linear_desc* desc, int rank, int nranks, int desc_is_full,
                                       mlxq_linear_t* out);
 MLXQ_API void mlxq_linear_destroy(mlxq_linear_t h);
+/* Load-time preparation (the place of `makePairs`, Transformer.swift:160-188, which repacks scales and biases once per
+ * layer): builds the private table of scales and biases that the tensor-core GEMM reads (out_dim * in_dim / 8 bytes of
+ * device memory owned by the handle) on `stream` and waits for it.  Optional: without it the first long batch builds
+ * the table (and when that is not possible -- a stream being captured, no memory -- every such batch stages it in
+ * scratch memory).  Results do not depend on it.  Layers the GEMM never takes are left untouched. */
+MLXQ_API int mlxq_linear_prepare(mlxq_linear_t h, mlxq_stream_t stream);
 
 /* Properties of `Linear` (Transformer.swift:16-23). */
 MLXQ_API int64_t mlxq_linear_in_dim(mlxq_linear_t h);
@@ -216,7 +222,9 @@ MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_str
  * The rows may be read by work enqueued on `stream` before this rank's NEXT fused call on the communicator, and only
  * by such work: calls alternate between two buffers, and a peer that runs ahead starts storing its second-next
  * call's rows into this buffer as soon as this rank has published its next call.
- * Every rank must issue the same sequence of fused calls.  Only shapes the persistent decode kernel serves
+ * Every rank must issue the same sequence of fused calls.  The calls may be captured into a CUDA graph and replayed
+ * (the call's number is kept on the device); a captured sequence must then hold an even number of fused calls of the
+ * communicator, so that the two buffers keep alternating from one replay to the next.  Only shapes the persistent decode kernel serves
  * (T <= 16, the usual alignment) are accepted; others return MLXQ_UNSUPPORTED and leave the communicator
  * untouched -- use mlxq_linear_forward_gather for those.  A wait for a peer gives up after two seconds:
  * the result is then incomplete and mlxq_stream_status reports MLXQ_TIMEOUT. */

@@ -43,6 +43,7 @@ SIGNATURES = {
     "mlxq_linear_create": (C.c_int, [C.POINTER(LinearDesc), C.POINTER(C.c_void_p)]),
     "mlxq_linear_create_shard": (C.c_int, [C.POINTER(LinearDesc), C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "mlxq_linear_destroy": (None, [C.c_void_p]),
+    "mlxq_linear_prepare": (C.c_int, [C.c_void_p, C.c_void_p]),
     "mlxq_linear_in_dim": (C.c_int64, [C.c_void_p]),
     "mlxq_linear_out_dim": (C.c_int64, [C.c_void_p]),
     "mlxq_linear_bits": (C.c_int, [C.c_void_p]),

@@ -196,7 +196,7 @@ static void fill_qmv(QmvParams& p, const mlxq_linear_t* parts, int n) {
     p.s_dtype = f->s_dtype;
     p.bias_dtype = f->bias_dtype;
     p.has_bias = f->bias != nullptr;
-    p.fast = fast && row_bytes(f) % 16 == 0 && env_long("MLXQ_QMV_FORCE_GENERIC", 0) == 0;
+    p.fast = fast && row_bytes(f) % 16 == 0;
     p.seg32 = f->gs % 32 == 0;
     p.gs_shift = -1;
     for (int s = 3; s < 31; s++) if ((1 << s) == f->gs) p.gs_shift = s;
@@ -279,6 +279,28 @@ static int gemm_tile_for(const mlxq_linear* h, int x_dtype, int64_t x_stride, co
     return qgemm_tile_tokens(gemm_layer(h), x_dtype, x_stride, x, T);
 }
 
+// The layer's GEMM table, built once (device memory owned by the handle).  Returns nullptr when it cannot be kept --
+// the stream is being captured, or the allocation failed -- and the GEMM then stages the table per call as before.
+// `allow_build` is false on the path that must not allocate.
+static const void* gemm_table_of(mlxq_linear* h, cudaStream_t st, bool allow_build) {
+    std::lock_guard<std::mutex> lk(h->table_mu);
+    if (h->gemm_table || h->table_tried || !allow_build) return h->gemm_table;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    h->table_tried = true;
+    const GemmLayer L = gemm_layer(h);
+    void* t = nullptr;
+    if (cudaMalloc(&t, qgemm_table_bytes(L)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    // built on the caller's stream and awaited once, so that calls on other streams may use it at once
+    if (qgemm_build_table(L, t, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(t);
+        return nullptr;
+    }
+    h->gemm_table = t;
+    return t;
+}
+
 int forward_impl(mlxq_linear_t h, cudaStream_t st, const void* x, int x_dtype, int64_t x_stride, void* y, int y_dtype,
                  int64_t y_stride, int64_t T, const PeerGather* peer) {
     if (!h) return fail(MLXQ_INVALID_ARGUMENT, "null layer");
@@ -293,6 +315,8 @@ int forward_impl(mlxq_linear_t h, cudaStream_t st, const void* x, int x_dtype, i
         GemmCall c;
         c.x = x; c.x_dtype = x_dtype; c.x_stride = x_stride; c.y = y; c.y_dtype = y_dtype; c.y_stride = y_stride; c.T = T;
         c.err = device_error_word(h->device);
+        if (!c.err) return fail(MLXQ_GPU_FAILURE, "no error word on device %d", h->device);
+        c.table = gemm_table_of(h, st, true);
         const char* why = "";
         cudaError_t err = launch_qgemm(gemm_layer(h), c, st, &why);
         if (err != cudaSuccess) return fail(MLXQ_GPU_FAILURE, "qgemm launch: %s (%s)", cudaGetErrorString(err), why);
@@ -373,7 +397,25 @@ int mlxq_linear_create_shard(const mlxq_linear_desc* desc, int rank, int nranks,
     return MLXQ_OK;
 }
 
-void mlxq_linear_destroy(mlxq_linear_t h) { delete h; }
+void mlxq_linear_destroy(mlxq_linear_t h) {
+    if (!h) return;
+    if (h->gemm_table) {
+        DeviceGuard guard(h->device);
+        cudaFree(h->gemm_table);
+    }
+    delete h;
+}
+
+int mlxq_linear_prepare(mlxq_linear_t h, mlxq_stream_t stream) {
+    if (!h) return fail(MLXQ_INVALID_ARGUMENT, "null layer");
+    DeviceGuard guard(h->device);
+    if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
+    if (qgemm_tile_tokens(gemm_layer(h), MLXQ_BF16, h->in_dim, nullptr, 1024) == 0) return MLXQ_OK;      // the GEMM never takes this layer
+    if (!gemm_table_of(h, static_cast<cudaStream_t>(stream), true))
+        return fail(MLXQ_OUT_OF_MEMORY, "%s: the GEMM's scale table (%zu bytes) could not be built ahead", h->name.c_str(),
+                    qgemm_table_bytes(gemm_layer(h)));
+    return MLXQ_OK;
+}
 
 int64_t mlxq_linear_in_dim(mlxq_linear_t h) { return h ? h->in_dim : 0; }
 int64_t mlxq_linear_out_dim(mlxq_linear_t h) { return h ? h->out_dim : 0; }
@@ -402,7 +444,8 @@ int mlxq_linear_forward_static(mlxq_linear_t h, mlxq_stream_t stream, const void
         if (need > qgemm_static_capacity())
             return fail(MLXQ_INVALID_ARGUMENT, "%s: T * in_dim * 2 = %llu bytes of staged activations exceed the %zu-byte static scratch; "
                         "split the batch or use mlxq_linear_forward", h->name.c_str(), need, qgemm_static_capacity());
-        const size_t table = qgemm_table_bytes(gemm_layer(h));
+        const void* kept = gemm_table_of(h, st, false);          // a table built ahead (mlxq_linear_prepare) needs no room
+        const size_t table = kept ? 0 : qgemm_table_bytes(gemm_layer(h));
         if (table > qgemm_static_table_capacity())
             return fail(MLXQ_INVALID_ARGUMENT, "%s: the layer's staged scale table (%zu bytes, out_dim * in_dim / 8 with rows rounded up to 256) "
                         "exceeds the %zu-byte static scratch; shard the layer or use mlxq_linear_forward", h->name.c_str(), table,
@@ -410,6 +453,8 @@ int mlxq_linear_forward_static(mlxq_linear_t h, mlxq_stream_t stream, const void
         GemmCall c;
         c.x = x; c.x_dtype = x_dtype; c.x_stride = x_stride; c.y = y; c.y_dtype = y_dtype; c.y_stride = y_stride; c.T = T;
         c.err = device_error_word(h->device);
+        if (!c.err) return fail(MLXQ_GPU_FAILURE, "no error word on device %d", h->device);
+        c.table = kept;
         const char* why = "";
         cudaError_t err = launch_qgemm_static(gemm_layer(h), c, st, &why);
         if (err != cudaSuccess) return fail(MLXQ_GPU_FAILURE, "qgemm launch: %s (%s)", cudaGetErrorString(err), why);
@@ -499,8 +544,10 @@ int mlxq_linear_lookup(mlxq_linear_t h, mlxq_stream_t stream, const int32_t* ids
     if (T < 0) return fail(MLXQ_INVALID_ARGUMENT, "T = %lld", (long long)T);
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
+    unsigned* errw = device_error_word(h->device);
+    if (!errw) return fail(MLXQ_GPU_FAILURE, "no error word on device %d", h->device);
     cudaError_t err = launch_lookup(h->w, h->s, h->b, h->s_dtype, ids, out, T, static_cast<int>(h->out_dim),
-                                    static_cast<int>(h->in_dim), h->gs, h->bits, device_error_word(h->device),
+                                    static_cast<int>(h->in_dim), h->gs, h->bits, errw,
                                     static_cast<cudaStream_t>(stream));
     return err == cudaSuccess ? MLXQ_OK : cuda_fail(err, "lookup launch");
 }

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 
 #include "peer_gather.h"
@@ -23,6 +24,11 @@ struct mlxq_linear {
     int shard_rank, shard_count;
     bool qmv_eligible;
     std::string name;
+    // The tensor-core GEMM's staged scale/bias table (it depends on the layer only): built by mlxq_linear_prepare or
+    // by the first batch that takes the GEMM, owned by the handle, freed with it.
+    std::mutex table_mu;
+    void* gemm_table = nullptr;
+    bool table_tried = false;
 };
 
 namespace mlxq {

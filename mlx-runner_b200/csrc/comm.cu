@@ -67,6 +67,7 @@ struct GatherWindow {
     unsigned* flags = nullptr;                   // this rank's flag array
     unsigned* peer_flags[mlxq::MAX_PEERS + 1] = {};
     unsigned* counter = nullptr;
+    unsigned* epoch_ctr = nullptr;               // completed fused calls, kept on the device (see PeerGather::epoch_ctr)
     size_t bytes = 0;
     unsigned epoch = 0;
 };
@@ -79,10 +80,13 @@ struct mlxq_comm {
 
 namespace {
 
-// One warp: lane p waits (bounded, two seconds) until peer p's flag in this rank's array has reached `epoch`.
-__global__ void gather_wait_kernel(const unsigned* my_flags, int rank, int nranks, unsigned epoch, unsigned* err) {
+// One warp: lane p waits (bounded, two seconds) until peer p's flag in this rank's array has reached the number of
+// this rank's completed fused calls (read from the device, so that the launch can be replayed from a graph).
+__global__ void gather_wait_kernel(const unsigned* my_flags, int rank, int nranks, const unsigned* epoch_ctr, unsigned* err) {
     const int p = threadIdx.x;
     if (p >= nranks || p == rank) return;
+    const unsigned epoch = *reinterpret_cast<const volatile unsigned*>(epoch_ctr);
+    if (epoch == 0u) return;
     unsigned long long t0, t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (;;) {
@@ -195,6 +199,7 @@ int mlxq_comm_window(mlxq_comm_t c, size_t bytes) {
     cudaMemset(w.local, 0, 2 * bytes);
     cudaMemset(w.flags, 0, 256);
     w.counter = w.flags + 32;
+    w.epoch_ctr = w.flags + 40;
     w.bytes = bytes;
     w.peer[c->rank] = w.local;
     w.peer_flags[c->rank] = w.flags;
@@ -248,9 +253,13 @@ int mlxq_linear_forward_gather_fused(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream
     mlxq::PeerGather pg = {};
     pg.rank = c->rank;
     pg.epoch = epoch;
-    pg.wait_epoch = w.epoch;          // the previous fused call: its rows may be this call's activations
     pg.my_flags = w.flags;
     pg.counter = w.counter;
+    pg.epoch_ctr = w.epoch_ctr;
+    {
+        const char* xp = static_cast<const char*>(x);
+        pg.x_is_gathered = (xp >= w.local && xp < w.local + 2 * w.bytes) ? 1 : 0;
+    }
     for (int p = 0; p < c->size; p++) {
         if (p == c->rank) continue;
         pg.y[pg.n] = w.peer[p] + half + static_cast<size_t>(h->row_offset) * 4;
@@ -273,7 +282,7 @@ int mlxq_comm_wait(mlxq_comm_t c, mlxq_stream_t stream) {
     if (e != cudaSuccess) return mlxq::cuda_fail(e, "cudaSetDevice");
     unsigned* err = mlxq::device_error_word(c->device);
     if (!err) return mlxq::fail(MLXQ_GPU_FAILURE, "no error word on device %d", c->device);
-    gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->win.flags, c->rank, c->size, c->win.epoch, err);
+    gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->win.flags, c->rank, c->size, c->win.epoch_ctr, err);
     e = cudaGetLastError();
     return e == cudaSuccess ? MLXQ_OK : mlxq::cuda_fail(e, "gather wait launch");
 }

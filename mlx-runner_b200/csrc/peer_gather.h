@@ -11,13 +11,17 @@ constexpr int MAX_PEERS = 7;   // ranks beside this one (8 GPUs of one box)
 struct PeerGather {
     int n;                          // peers written beside the local y (0: plain call)
     int rank;                       // this rank: the slot it owns in every rank's flag array
-    unsigned epoch;                 // number of this gather call on the communicator (same on every rank)
-    unsigned wait_epoch;            // before reading x, wait until every peer has finished this earlier call (0: none)
+    unsigned epoch;                 // number of this gather call on the communicator (same on every rank); before it reads x the
+                                    // kernel waits until every peer has finished call epoch - 1 (whose rows may be this call's x)
     char* y[MAX_PEERS];             // the local y pointer's twin inside each peer's window
     unsigned* flag[MAX_PEERS];      // each peer's flag array
     int peer_rank[MAX_PEERS];
     unsigned* my_flags;             // this rank's flag array: slot r holds the last epoch rank r finished
     unsigned* counter;              // CTAs of the running call that have stored all their rows (wraps at the grid size)
+    int x_is_gathered;              // the activations lie in this rank's gather window (a previous call's output): wait for
+                                    // the peers before reading them; otherwise the wait is put off until the first row is stored
+    unsigned* epoch_ctr;            // device word holding the number of completed gather calls; when set, the kernel takes
+                                    // its epoch from it (completed + 1) instead of `epoch`, so that a captured launch can be replayed
 };
 
 }  // namespace mlxq

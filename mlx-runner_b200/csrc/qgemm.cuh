@@ -25,6 +25,7 @@ struct GemmCall {
     long long y_stride;
     long long T;
     unsigned* err;       // device error word
+    const void* table;   // the layer's staged scale/bias table when it has been built ahead (qgemm_build_table), else nullptr
 };
 
 // 0 when the GEMM cannot take this layer / call (the caller then uses the CUDA-core kernel), else the
@@ -37,6 +38,9 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
 // The same GEMM with its scratch in a fixed device array instead of pool memory: allocates nothing.
 // Returns cudaErrorInvalidValue (why = "batch exceeds the static scratch") beyond qgemm_static_capacity().
 size_t qgemm_static_capacity();
+// Builds the layer's staged scale/bias table (qgemm_table_bytes(L) bytes at `table`, 256-byte aligned) on `st`.  The
+// table depends on the layer only: a caller that keeps it passes it in GemmCall::table and saves the GEMM the work.
+cudaError_t qgemm_build_table(const GemmLayer& L, void* table, cudaStream_t st);
 // Bytes of the scale/bias table the GEMM stages for this layer, and the room the fixed array has for it.
 size_t qgemm_table_bytes(const GemmLayer& L);
 size_t qgemm_static_table_capacity();

@@ -148,6 +148,10 @@ qgemm4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+    // Launched as a programmatic dependent of the pre-pass: the set-up above and the weight producer's first slabs
+    // (the layer's constants) run while it finishes; every other role first waits for it (staged activations, the
+    // scale/bias table, and -- through the pre-pass's own ordering -- everything earlier in the stream).
+    if (warp != W_PRODUCER) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ---- TMA producer ----------------------------------------------------------------------------------
@@ -468,6 +472,10 @@ qgemm4w_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+    // Launched as a programmatic dependent of the pre-pass: the set-up above and the weight producer's first slabs
+    // (the layer's constants) run while it finishes; every other role first waits for it (staged activations, the
+    // scale/bias table, and -- through the pre-pass's own ordering -- everything earlier in the stream).
+    if (warp != W_PRODUCER) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ---- TMA producer of the activations: one 256-token x 64 box per stage --------------------------------------
@@ -770,6 +778,9 @@ struct StageArgs {
     unsigned x_blocks;
 };
 __global__ void stage_inputs_kernel(const StageArgs g) {
+    // the GEMM that follows is launched as a programmatic dependent: it may set up (barriers, tensor memory, first
+    // weight slabs) while this grid runs, and waits for this grid before it touches what is written here
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (blockIdx.x < g.x_blocks) stage_x_part(g.x, g.is_bf16, g.x_stride, g.xs, g.T, g.K, blockIdx.x, g.x_blocks);
     else stage_scales_part(g.s, g.b, g.s_dtype, g.O, g.o_pad, g.gpr, g.gs_shift, g.k_stages, g.n_slabs, g.pairs,
                            blockIdx.x - g.x_blocks, gridDim.x - g.x_blocks);
@@ -895,7 +906,8 @@ cudaError_t enqueue_gemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     const int bm = wide_tile ? wide::BM : BM, bn = wide_tile ? wide::BN : BN;
     a.m_tiles = (L.O + bm - 1) / bm;
     a.n_tiles = static_cast<int>((c.T + bn - 1) / bn);
-    a.pairs = pairs;
+    const bool have_table = c.table != nullptr;
+    a.pairs = have_table ? static_cast<const uint4*>(c.table) : pairs;
     a.o_pad = (L.O + BM - 1) / BM * BM;          // the table is padded to the tall tile's 256 rows for both
     const int k_stages = L.K / BK, n_slabs = (k_stages + W_SPAN - 1) / W_SPAN;
     {
@@ -906,7 +918,8 @@ cudaError_t enqueue_gemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
         g.s = L.s; g.b = L.b; g.s_dtype = L.s_dtype; g.O = L.O; g.o_pad = a.o_pad; g.gpr = L.K / L.gs; g.gs_shift = a.gs_shift;
         g.k_stages = k_stages; g.n_slabs = n_slabs; g.pairs = pairs;
         g.x_blocks = static_cast<unsigned>(n / 256 + 1 < 148LL * 6 ? n / 256 + 1 : 148LL * 6);
-        const unsigned s_blocks = static_cast<unsigned>(ns / 256 + 1 < 148LL * 4 ? ns / 256 + 1 : 148LL * 4);
+        // (the table part is left out when the layer's table was built ahead)
+        const unsigned s_blocks = have_table ? 0u : static_cast<unsigned>(ns / 256 + 1 < 148LL * 4 ? ns / 256 + 1 : 148LL * 4);
         stage_inputs_kernel<<<g.x_blocks + s_blocks, 256, 0, st>>>(g);
     }
     CUtensorMap map_w, map_x;
@@ -925,13 +938,34 @@ cudaError_t enqueue_gemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     a.idesc = (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
     const long long tiles = static_cast<long long>(a.m_tiles) * a.n_tiles;
     const int sms = sm_count(L.device);
-    const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-    if (wide_tile) wide::qgemm4w_kernel<<<grid, NUM_THREADS, wide::SMEM_BYTES, st>>>(map_w, map_x, a);
-    else qgemm4_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles < sms ? tiles : sms));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = wide_tile ? wide::SMEM_BYTES : SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute la[1];
+    la[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;       // a dependent of the pre-pass, see the kernels
+    la[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = la;
+    cfg.numAttrs = 1;
+    if (wide_tile) return cudaLaunchKernelEx(&cfg, wide::qgemm4w_kernel, map_w, map_x, a);
+    return cudaLaunchKernelEx(&cfg, qgemm4_kernel, map_w, map_x, a);
 }
 
 }  // namespace
+
+cudaError_t qgemm_build_table(const GemmLayer& L, void* table, cudaStream_t st) {
+    int gs_shift = 0;
+    while ((1 << gs_shift) < L.gs) gs_shift++;
+    const int k_stages = L.K / BK, n_slabs = (k_stages + W_SPAN - 1) / W_SPAN;
+    StageArgs g = {};
+    g.s = L.s; g.b = L.b; g.s_dtype = L.s_dtype; g.O = L.O; g.o_pad = (L.O + BM - 1) / BM * BM; g.gpr = L.K / L.gs; g.gs_shift = gs_shift;
+    g.k_stages = k_stages; g.n_slabs = n_slabs; g.pairs = static_cast<uint4*>(table);
+    g.x_blocks = 0;
+    const long long ns = static_cast<long long>(n_slabs) * g.o_pad;
+    stage_inputs_kernel<<<static_cast<unsigned>(ns / 256 + 1 < 148LL * 4 ? ns / 256 + 1 : 148LL * 4), 256, 0, st>>>(g);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st, const char** why) {
     *why = "";
@@ -940,7 +974,7 @@ cudaError_t launch_qgemm(const GemmLayer& L, const GemmCall& c, cudaStream_t st,
     cudaMemPool_t pool = scratch_pool(L.device);
     if (!pool) { *why = "scratch pool"; return cudaErrorMemoryAllocation; }
     uint8_t* scratch = nullptr;
-    cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), x_bytes(L, c.T) + table_bytes(L), pool, st);
+    cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), x_bytes(L, c.T) + (c.table ? 0 : table_bytes(L)), pool, st);
     if (e != cudaSuccess) { *why = "scratch allocation"; return e; }
     const cudaError_t launched = enqueue_gemm(L, c, st, reinterpret_cast<__half*>(scratch),
                                               reinterpret_cast<uint4*>(scratch + x_bytes(L, c.T)), why);
@@ -971,7 +1005,7 @@ cudaError_t launch_qgemm_static(const GemmLayer& L, const GemmCall& c, cudaStrea
         *why = "batch exceeds the static scratch";
         return cudaErrorInvalidValue;
     }
-    if (table_bytes(L) > STATIC_TABLE_BYTES) {
+    if (!c.table && table_bytes(L) > STATIC_TABLE_BYTES) {
         *why = "the layer's scale table exceeds the static scratch";
         return cudaErrorInvalidValue;
     }

@@ -301,11 +301,21 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
 
     // ---- the activations: nothing before this line reads x, e or writes y --------------------------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (q.peer.n > 0 && q.peer.wait_epoch != 0) {
-        // the activations may be the previous sharded call's gathered output: every peer must have finished it
-        if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], q.peer.wait_epoch, p.err);
-        __syncthreads();
+    unsigned peer_epoch = q.peer.epoch;
+    if (q.peer.n > 0) {
+        // The call's number on the communicator: from the device-side count of completed calls when there is one (the
+        // previous grid, which wrote it, is complete here), so that a launch captured in a graph stays correct on replay.
+        if (q.peer.epoch_ctr != nullptr) peer_epoch = *reinterpret_cast<volatile unsigned*>(q.peer.epoch_ctr) + 1u;
+        if (peer_epoch != 1u && q.peer.x_is_gathered) {
+            // the activations are the previous sharded call's gathered output: every peer must have finished it
+            if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
+            __syncthreads();
+        }
     }
+    // Otherwise the wait for the peers' previous call only guards their window buffers (this call's rows go where the
+    // rows of the call before the previous one were, which a peer may read until its previous call has run): it is
+    // put off until a warp stores its first rows, by when the peers' flags have usually arrived.
+    bool peers_ready = q.peer.n == 0 || q.peer.x_is_gathered || peer_epoch == 1u;
     {
         // staged once per CTA: fp16, permuted and pre-scaled to match the A registers (see qmv_mma.cuh), eight
         // values per thread and turn.  The chunks of a group sit in consecutive lanes, so the per-group sums come
@@ -545,6 +555,11 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         if (ks > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(ks * 32) : "memory");
         else __syncwarp();
         if (kw == 0) {
+            if (!peers_ready) {
+                if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
+                __syncwarp();
+                peers_ready = true;
+            }
             for (int idx = lane; idx < 16 * T; idx += 32) {
                 const int tok = idx >> 4, r = idx & 15;
                 const int row = c_blk * 16 + r;
@@ -573,7 +588,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         // publishes this rank's epoch in every peer's flag array.  Nobody waits here: the next call on the
         // communicator (or mlxq_comm_wait) waits for the peers' flags before it reads the gathered rows,
         // and by then its own weight copies are already in flight.
-        __threadfence_system();
+        if (kw == 0) __threadfence_system();                    // (only a group's first warp stored rows)
         __syncthreads();
         if (warp == 0) {
             unsigned fin = 0;
@@ -582,7 +597,8 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             if (fin) {
                 __threadfence_system();
                 if (lane < q.peer.n)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(q.peer.flag[lane] + q.peer.rank), "r"(q.peer.epoch) : "memory");
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(q.peer.flag[lane] + q.peer.rank), "r"(peer_epoch) : "memory");
+                if (lane == 0 && q.peer.epoch_ctr != nullptr) *reinterpret_cast<volatile unsigned*>(q.peer.epoch_ctr) = peer_epoch;
             }
         }
     }

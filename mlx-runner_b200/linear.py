@@ -238,6 +238,11 @@ class Linear:
         check(L.load().mlxq_linear_forward(self._h, _stream_handle(stream), _ptr(x), _act_dtype(x, xDtype), xStride,
                                            _ptr(y), _act_dtype(y, yDtype), yStride, T))
 
+    def prepare(self, stream=None) -> None:
+        """Load-time preparation (the place of ``makePairs``, ``Transformer.swift:160-188``): builds the GEMM's private
+        table of scales and biases ahead of the first long batch.  Optional; results do not depend on it."""
+        check(L.load().mlxq_linear_prepare(self._h, _stream_handle(stream)))
+
     def encodeStatic(self, stream, x, xStride: int, y, yStride: int, T: int, xDtype: Optional[int] = None,
                      yDtype: Optional[int] = None) -> None:
         """``encode`` for hosts that must not allocate device memory while they run: the GEMM's staged copy

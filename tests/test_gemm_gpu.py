@@ -136,3 +136,61 @@ def test_gemm_repeats_bit_for_bit_at_full_size(mlxq):
         differing = int((ys[1].view(torch.int32) != ys[0].view(torch.int32)).sum())
         assert differing == 0, f"call {call}: {differing} outputs differ from the first call's"
     mlxq.streamStatus(None, 0)
+
+
+def _bf16_bits(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.int64)
+
+
+@pytest.mark.parametrize("O,K", [(14336, 4096), (4096, 14336)])
+def test_gemm_prefill_sizes_against_oracle(mlxq, oracle, O, K):
+    # the prefill configuration at its own sizes: M = 128, 512, 8192 on both orientations (M = 2048 is covered above);
+    # the oracle on a sample of rows x tokens.  fp32 output: the 1e-3 bar.  bf16 output: within one bf16 ulp of the
+    # oracle rounded to bf16 (outputs so close to zero that an ulp is below the fp32 bar are held to that bar instead).
+    lay = synth.make_layer(O, K, 4, 64, synth.BF16, seed=O % 97, keep_codes=False)
+    layer = DevLayer(mlxq, lay.packed, lay.scales_raw, lay.biases_raw, synth.BF16, K)
+    g = np.random.default_rng(K)
+    rows = np.sort(g.choice(O, size=48, replace=False))
+    for T in (128, 512, 8192):
+        _, x = synth.make_activations(T, K, synth.BF16, seed=T)
+        toks = np.sort(np.concatenate([np.arange(8), g.choice(np.arange(8, T), size=24, replace=False)]))
+        ref = oracle.qmatmul(lay.packed[rows], lay.scales_raw[rows], lay.biases_raw[rows], synth.BF16, x[toks], K, 4, 64)
+        assert layer.linear.kernelFor(T, 2, 0) == "qgemm"
+        got = run(layer, x, T, x_dtype=2)[toks][:, rows]
+        err = oracle.max_rel_err(got, ref)
+        assert err < 1e-3, f"{O}x{K} T={T}: max relative error {err}"
+        got16 = run(layer, x, T, x_dtype=2, y_dtype=2)[toks][:, rows]
+        ulps = np.abs(_bf16_bits(got16) - _bf16_bits(ref))
+        near_zero = np.abs(got16 - ref) <= 1e-3 * np.maximum(1.0, np.abs(ref))
+        assert np.all((ulps <= 1) | near_zero), f"{O}x{K} T={T}: bf16 output off by {int(ulps[~near_zero].max())} ulps"
+    mlxq.streamStatus(None, 0)
+
+
+def test_prepared_table_changes_nothing(mlxq, oracle):
+    # mlxq_linear_prepare builds the GEMM's scale/bias table ahead; a batch encoded while its stream is being captured
+    # cannot keep a table and stages it per call.  All routes must give the same bits.
+    O, K, T = 768, 2048, 160
+    lay = synth.make_layer(O, K, 4, 64, synth.BF16, seed=77, bias_noise=True)
+    _, xv = synth.make_activations(T, K, synth.BF16, seed=5)
+    x = torch.from_numpy(xv).to("cuda").to(torch.bfloat16)
+    outs = []
+    for route in ("prepared", "first call builds it", "captured"):
+        layer = DevLayer(mlxq, lay.packed, lay.scales_raw, lay.biases_raw, synth.BF16, K, name=route)
+        y = torch.full((T, O), float("nan"), dtype=torch.float32, device="cuda")
+        if route == "prepared":
+            layer.linear.prepare(None)
+        if route == "captured":
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                layer.linear.encode(torch.cuda.current_stream(), x, K, y, O, T)
+            g.replay()
+        else:
+            layer.linear.encode(None, x, K, y, O, T)
+        torch.cuda.synchronize()
+        mlxq.streamStatus(None, 0)
+        outs.append(y.cpu().numpy())
+    ref = oracle.qmatmul(lay.packed, lay.scales_raw, lay.biases_raw, synth.BF16, xv, K, 4, 64)
+    assert oracle.max_rel_err(outs[0], ref) < 1e-3
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    assert np.array_equal(outs[0].view(np.uint32), outs[2].view(np.uint32))

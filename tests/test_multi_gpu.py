@@ -69,6 +69,52 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         assert oracle.max_rel_err(out.cpu().numpy(), fx.reference(x)) < 1e-3
         dist.barrier()
+        # A chain: the gathered rows of one fused call are the activations of the next, with no wait between them
+        # (the second call itself waits for the peers' rows before it reads them), then two more links.
+        K2 = O                                                              # 384 rows gathered -> 384 inputs
+        fx2 = oracle.QuantFixture(O=O, K=K2, bits=bits, gs=gs, seed=12)
+        w2 = torch.from_numpy(fx2.packed.view(np.int32).reshape(O, -1)).to(dev)
+        s2 = torch.from_numpy(fx2.scales_raw.view(np.int16)).to(dev).view(torch.float16)
+        b2 = torch.from_numpy(fx2.biases_raw.view(np.int16)).to(dev).view(torch.float16)
+        lin2 = mlxq.Linear.shard(w2, s2, b2, None, inDim=K2, rank=rank, nranks=world, full=True, name="shard2", device=rank)
+        x = oracle.RNG(123).floats(K).reshape(1, K).astype(np.float32)
+        h = comm.forwardGatherFused(lin, None, torch.from_numpy(x).to(dev), K, 1, wait=False)
+        ref = fx.reference(x)
+        for _ in range(3):
+            h = comm.forwardGatherFused(lin2, None, h, K2, 1, wait=False)
+            ref = fx2.reference(ref)
+        comm.wait(None)
+        torch.cuda.synchronize()
+        mlxq.streamStatus(None, rank)
+        assert oracle.max_rel_err(h.cpu().numpy(), ref) < 1e-3, f"rank {rank}: chained fused calls"
+        dist.barrier()
+        # The same two calls captured into a CUDA graph and replayed with new activations: the call numbers come from
+        # the device, so every replay waits for its own peers' rows.
+        x_buf = torch.zeros((1, K), dtype=torch.float32, device=dev)
+        keep = torch.zeros((1, O), dtype=torch.float32, device=dev)
+        x_buf.copy_(torch.from_numpy(x).to(dev))
+        for _ in range(2):                                                   # warm-up outside the capture (even count)
+            comm.forwardGatherFused(lin, None, x_buf, K, 1, wait=False)
+        comm.wait(None)
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            st = torch.cuda.current_stream()
+            h1 = comm.forwardGatherFused(lin, st, x_buf, K, 1, wait=False)
+            h2 = comm.forwardGatherFused(lin2, st, h1, K2, 1, wait=False)
+            comm.wait(st)
+            keep.copy_(h2)
+        for rep in range(3):
+            xr = oracle.RNG(200 + rep).floats(K).reshape(1, K).astype(np.float32)
+            x_buf.copy_(torch.from_numpy(xr).to(dev))
+            g.replay()
+            torch.cuda.synchronize()
+            mlxq.streamStatus(None, rank)
+            want = fx2.reference(fx.reference(xr))
+            assert oracle.max_rel_err(keep.cpu().numpy(), want) < 1e-3, f"rank {rank}: graph replay {rep}"
+            dist.barrier()
+        del g
         comm.close()
         dist.destroy_process_group()
         q.put((rank, "ok"))
@@ -93,3 +139,26 @@ def test_sharded_decode_nccl_and_fused_gather_on_two_gpus():
     for p in procs:
         p.join(timeout=60)
     assert all(v == "ok" for v in results.values()), "\n".join(f"rank {k}: {v}" for k, v in results.items())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_layers_on_two_devices():
+    # the kernels' shared-memory opt-in is per device: a process that holds layers on two GPUs must be able to run both
+    mlxq = importlib.import_module("mlx-runner_b200")
+    from oracle import oracle
+    fx = oracle.QuantFixture(O=256, K=1024, bits=4, gs=64, seed=5)
+    x = oracle.RNG(6).floats(2 * 1024).reshape(2, 1024).astype(np.float32)
+    ref = fx.reference(x)
+    for d in (0, 1, 0):
+        dev = f"cuda:{d}"
+        w = torch.from_numpy(fx.packed.view(np.int32).reshape(256, -1)).to(dev)
+        s = torch.from_numpy(fx.scales_raw.view(np.int16)).to(dev).view(torch.float16)
+        b = torch.from_numpy(fx.biases_raw.view(np.int16)).to(dev).view(torch.float16)
+        lin = mlxq.Linear(w, s, b, None, inDim=1024, name=f"dev{d}", device=d)
+        for T in (1, 2):
+            y = torch.full((T, 256), float("nan"), dtype=torch.float32, device=dev)
+            with torch.cuda.device(d):
+                lin.encode(None, torch.from_numpy(x[:T]).to(dev), 1024, y, 256, T)
+                torch.cuda.synchronize()
+            mlxq.streamStatus(None, d)
+            assert oracle.max_rel_err(y.cpu().numpy(), ref[:T]) < 1e-3, f"device {d} T={T}"
