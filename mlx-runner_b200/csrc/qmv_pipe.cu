@@ -148,7 +148,16 @@ size_t qmv_pipe_plan(int bits, const MmaParams& p, int tokens, int sms, PipePlan
             pairs = pairs && (c0 & 255) == (c1 & 255) && g1 == g0 + 1 && (g0 & 1) == 0 && g0 == static_cast<int>((f0 >> 8) & 255);
         }
     pp.async_sb = pairs ? 1 : 0;
-    pp.special = (tokens == 1 && p.split == 1 && p.xn == 1 && pp.async_sb && pp.rowsum && (q.gs == 32 || q.gs == 64 || q.gs == 128)) ? q.gs : 0;
+    // (the one-token kernels assume slices of whole drain cycles)
+    bool whole_cycles = true;
+    {
+        const int spc = p.cycle << p.spg_shift;
+        for (int kw = 0; kw < pp.ks; kw++) {
+            const int a = ((nblk * kw) >> pp.ks_shift) << p.spg_shift, b = ((nblk * (kw + 1)) >> pp.ks_shift) << p.spg_shift;
+            if (a % spc != 0 || b % spc != 0) whole_cycles = false;
+        }
+    }
+    pp.special = (whole_cycles && tokens == 1 && p.split == 1 && p.xn == 1 && pp.async_sb && pp.rowsum && (q.gs == 32 || q.gs == 64 || q.gs == 128)) ? q.gs : 0;
     int off = align_up(p.xn * pp.xstride * 2, 16);
     pp.off_xsum = off; off += align_up(p.xn * groups * 4, 16);
     pp.off_zero = off; off += PIPE_ZERO_BYTES;

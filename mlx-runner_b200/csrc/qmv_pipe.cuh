@@ -136,6 +136,34 @@ __device__ __forceinline__ void stage8v(__half* col, int k, const float (&v)[8])
     }
 }
 
+// stage8v for fp16 activations that are staged as they are (one staged column per token): the eight halves arrive as
+// four words (x0,x1)(x2,x3)(x4,x5)(x6,x7) and leave permuted by byte permutes, the pre-scaling by a power of two is a
+// half2 multiply -- the same values as the fp32 route (scaling by a power of two, then one rounding to fp16).
+template <int BITS>
+__device__ __forceinline__ void stage8v_f16(__half* col, int k, const uint32_t (&w)[4]) {
+    static_assert(BITS != 2, "2-bit units span sixteen values");
+    uint4 o;
+    if constexpr (BITS == 4) {
+        // order 0,4,1,5,2,6,3,7; the odd codes of a byte sit four bits up: their activations are divided by 16
+        const __half2 sc = __floats2half2_rn(0.0625f, 0.0625f);
+        const uint32_t a = __byte_perm(w[0], w[2], 0x7632), b = __byte_perm(w[1], w[3], 0x7632);
+        const __half2 as = __hmul2(*reinterpret_cast<const __half2*>(&a), sc), bs = __hmul2(*reinterpret_cast<const __half2*>(&b), sc);
+        o.x = __byte_perm(w[0], w[2], 0x5410);
+        o.y = *reinterpret_cast<const uint32_t*>(&as);
+        o.z = __byte_perm(w[1], w[3], 0x5410);
+        o.w = *reinterpret_cast<const uint32_t*>(&bs);
+    } else if constexpr (BITS == 8) {
+        // order 0,2,1,3 inside every four
+        o.x = __byte_perm(w[0], w[1], 0x5410);
+        o.y = __byte_perm(w[0], w[1], 0x7632);
+        o.z = __byte_perm(w[2], w[3], 0x5410);
+        o.w = __byte_perm(w[2], w[3], 0x7632);
+    } else {
+        o = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    *reinterpret_cast<uint4*>(col + k) = o;
+}
+
 constexpr int pipe_log2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
 
 // GS = 0: any call, the column plan is read from the launch parameters.  GS = 32, 64, 128: the one-token call with
@@ -152,6 +180,12 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     constexpr int SP_GSH = !SP ? 0 : (KB > GS ? pipe_log2(KB / GS) : 0);      // log2(groups per step)
     constexpr int SP_SPG = !SP ? 0 : (GS > KB ? pipe_log2(GS / KB) : 0);      // log2(steps per group)
     constexpr int SP_CY = !SP ? 1 : ((8 >> SP_GSH) > 0 ? (8 >> SP_GSH) : 1);  // group blocks per drain cycle
+    // One-token plan: every slice holds whole drain cycles of SP_SPC steps (the planner sees to it) and starts on a
+    // multiple of UNR, so within a loop turn only the last step can close a cycle when UNR divides SP_SPC; and both halves
+    // of a step's MMAs read the same group when a lane's run does not straddle groups.
+    constexpr int SP_SPC = SP_CY << SP_SPG;
+    constexpr bool LAST_ONLY = SP && SP_SPC % UNR == 0;
+    constexpr bool SAME_AB = SP && CL <= GS;
     constexpr int NT = PIPE_WARPS * 32;
     constexpr int DEPTH = PIPE_DEPTH;
     constexpr uint32_t SB_OFF = 2 * 32 * LB;                   // (scale, bias) pairs follow the weights in a slot
@@ -256,6 +290,9 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             }
         }
     };
+    // from the end of this warp's slice of one block to its start in the group's next block, in bytes
+    const long long w_jump = static_cast<long long>(blk_stride) * 16 * static_cast<long long>(row_bytes) - static_cast<long long>(nsteps) * (4 * LB);
+    const long long s_jump = static_cast<long long>(blk_stride) * 16 * groups * sbytes;
     // copies of the UNR steps under the load cursor into the slots that start at `dst`, one commit group; moves the cursor on
     auto issue_turn = [&](uint32_t dst) {
         if (l_left > 0) {
@@ -273,7 +310,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                     });
                 }
                 const int ls = l_s + i;
-                if (async_sb && ((((ls + 1) & dmask) == 0) || ls + 1 == s_end)) {
+                if (async_sb && (!LAST_ONLY || i == UNR - 1) && ((((ls + 1) & dmask) == 0) || (!SP && ls + 1 == s_end))) {
                     // the step closes a drain cycle: the pair (g0, g0 + 1) is fetched when either group lies inside this
                     // warp's slice up to this step
                     const int g0 = (((ls & ~dmask) * KB) >> gs_shift) + pair_off;
@@ -290,7 +327,15 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             l_w[0] += UNR * 4 * LB; l_w[1] += UNR * 4 * LB;
             if (l_s == s_end) {
                 l_s = s_begin; l_blk += blk_stride;
-                if (l_left > 0) load_rows(l_blk);
+                if (l_left > 0) {
+                    if (q.n_parts == 1 && l_blk * 16 + 16 <= q.total_rows) {
+                        // one part, a whole block inside the layer: the next block's rows are a constant distance on
+                        l_w[0] += w_jump; l_w[1] += w_jump;
+                        if (async_sb) { l_sp[0] += s_jump; l_sp[1] += s_jump; l_bp[0] += s_jump; l_bp[1] += s_jump; }
+                    } else {
+                        load_rows(l_blk);
+                    }
+                }
             }
         }
         cp_commit();
@@ -326,7 +371,18 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             const int idx = base + threadIdx.x;
             const int tok = T == 1 ? 0 : pp.cpr_shift >= 0 ? idx >> pp.cpr_shift : idx / cpr, k = (idx - tok * cpr) * 8;
             float sum = 0.0f;
-            if (idx < total_chunks) {
+            if (idx < total_chunks && BITS != 2 && split == 1 && q.x_dtype == DT_F16) {
+                // fp16 activations stay fp16: permute and pre-scale the words, the sum alone is formed in fp32
+                const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k));
+                const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[i]));
+                    sum += f.x;
+                    sum += f.y;
+                }
+                if constexpr (BITS != 2) stage8v_f16<BITS>(xs + static_cast<size_t>(tok) * pp.xstride, k, w4);
+            } else if (idx < total_chunks) {
                 float v[8];
                 load8_coherent(q.x, q.x_dtype, static_cast<size_t>(tok) * q.x_stride + k, v);
 #pragma unroll
@@ -396,7 +452,8 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             // the turn's UNR steps have landed: their words (and, for steps that close a drain cycle, the pairs) to registers
             asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH / UNR - 1) : "memory");
             uint32_t w[UNR][2][NW];
-            uint32_t sbv[UNR][4];
+            uint32_t sbv[UNR][4];                                // (read only where drains[i] holds)
+            bool drains[UNR];
             static_for<0, UNR, 1>([&](auto ic) {
                 constexpr int i = decltype(ic)::value;
                 if constexpr (LB == 16) {
@@ -414,8 +471,8 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                     });
                 }
                 const int s = s0 + i;
-                sbv[i][0] = sbv[i][1] = sbv[i][2] = sbv[i][3] = 0u;
-                if (async_sb && (((s + 1) & dmask) == 0 || s + 1 == s_end)) {
+                drains[i] = (!LAST_ONLY || i == UNR - 1) && (((s + 1) & dmask) == 0 || (!SP && s + 1 == s_end));
+                if (async_sb && drains[i]) {
                     const uint32_t d = c_src + sb_delta;
                     asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[i][0]) : "r"(d), "n"(i * SLOT));
                     asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(sbv[i][1]) : "r"(d), "n"(i * SLOT + 128));
@@ -426,7 +483,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             static_for<0, UNR, 1>([&](auto ic) {
                 constexpr int i = decltype(ic)::value;
                 const int s = s0 + i;
-                const bool drain = ((s + 1) & dmask) == 0 || s + 1 == s_end;
+                const bool drain = drains[i];
                 const int cyc_s = (s >> spg_shift) & cyc_mask;
                 // lanes whose accumulator column belongs to another group (or cycle) multiply by zeros: they read
                 // them from a zeroed patch of shared memory, so the loads need no branch
@@ -434,7 +491,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
 #pragma unroll
                 for (int ps = 0; ps < NP; ps++) {
                     pa[ps] = b_on_a[ps] == cyc_s ? baddr[ps] + koff2 : zaddr;
-                    pb[ps] = b_on_b[ps] == cyc_s ? baddr[ps] + koff2 : zaddr;
+                    pb[ps] = SAME_AB ? pa[ps] : b_on_b[ps] == cyc_s ? baddr[ps] + koff2 : zaddr;
                 }
                 static_for<0, NM, 2>([&](auto jc) {
                     constexpr int j = decltype(jc)::value;

@@ -61,10 +61,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* a
 // Whole-warp wait for code that goes on to a ".sync.aligned" instruction (tcgen05.ld / tcgen05.st / mma.sync).
 // Lane 0 polls alone (bounded, like mbar_wait) and the verdict is broadcast; __syncwarp orders the other lanes'
 // later reads after lane 0's acquire.  Must be called by all 32 lanes.
-// Measured on B200: with every lane polling (mbarrier.try_wait suspends and resumes lanes one by one), a
-// tcgen05.st issued afterwards lost the data of some lanes of the warp now and then -- with a vote after the
-// loop, with __syncwarp, and even with the vote inside the loop.  One polling lane per warp has not failed in
-// thousands of full-size calls; tests/test_gemm_gpu.py repeats one and compares bit for bit.
+//
+// Why one lane.  With every lane running its own mbar_wait before a tcgen05.st, the store now and then lost the
+// data of some lanes (measured on B200, at full GEMM size only).  Read against the PTX rules, the all-lanes form
+// was in order on three counts: the phase parity is computed from warp-uniform counters, so no lane can wait for a
+// different phase; the barrier cannot advance twice while a lane of the warp still waits (the next phase needs this
+// warp's own arrival on full_a); and tcgen05.fence::after_thread_sync stood between the wait and the store.  What the
+// all-lanes form does differently is control flow: mbar_wait has two exits per lane (try_wait succeeded at once, or
+// the out-of-line slow path returned), lanes take them at different times, and everything after them -- including the
+// inline-asm store -- is reached through per-lane branches.  A ".sync.aligned" instruction must be executed by all
+// lanes of the warp as ONE instruction; inline asm is not marked convergent for the compiler, so it may legally be
+// cloned into both exits, and lanes arriving from different exits then run different copies of the store.  A
+// __syncwarp or a vote between the wait and the store synchronises the lanes in time but does not undo such cloning,
+// which fits the observation that neither cured it.  Whether that is the whole cause could not be confirmed (machine
+// code is not inspected here, and the failing form is not run again); the single-poller form removes the per-lane
+// branches from the path altogether -- the store is reached by straight-line code behind a shuffle -- and has not
+// failed; tests/test_gemm_gpu.py repeats a full-size call twelve times and compares bit for bit.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* abort_flag, unsigned* err) {
     int got = 1;
     if ((threadIdx.x & 31) == 0) got = mbar_wait(bar, parity, abort_flag, err) ? 1 : 0;
