@@ -37,10 +37,10 @@ sys.path.insert(0, ROOT)
 
 O_ROWS, K_COLS, BITS, GS = 11008, 4096, 4, 64
 LAYERS = 16          # distinct weight sets per pass; --layers overrides it (profiling runs use fewer)
-PASSES = 40          # passes per step: 640 launches, ~5 ms of device time
+PASSES = 48          # passes per step: 768 launches, ~6 ms of device time
 # DRAM bytes one launch of the decode kernel moved in an ncu capture of this workload's kernel at this shape
 # (dram__bytes_read.sum + dram__bytes_write.sum); reported as roofline.traffic for that shape on one GPU only.
-NCU_DRAM_BYTES_PER_LAUNCH = 25442048
+NCU_DRAM_BYTES_PER_LAUNCH = 25403904
 NCU_TRAFFIC_SOURCE = "ncu capture summarised in profiles/qmv_pipe_b4g64_m1.md (not measured in this run)"
 METRIC = "decode_qmv_hbm_gbs"
 UNIT = "GB/s"
@@ -636,7 +636,7 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="print the decode sweep table (bits x group x M) instead of the JSON line")
     ap.add_argument("--no-graph", action="store_true", help="time plain API calls instead of a replayed CUDA graph")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight sets per pass (default 16)")
-    ap.add_argument("--passes", type=int, default=PASSES, help="passes over the weight sets per step (default 40)")
+    ap.add_argument("--passes", type=int, default=PASSES, help="passes over the weight sets per step (default 48)")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)

@@ -105,6 +105,7 @@ size_t qmv_pipe_plan(int bits, const MmaParams& p, int tokens, int sms, PipePlan
     const int warps = PIPE_WARPS;
     // K split: the group size that leaves the longest-working warp the least to do
     const int cta_blocks = (pp.n_blocks + pp.grid - 1) / pp.grid;
+    const int step_weight = bits == 4 ? 4 : bits == 8 ? 3 : bits == 2 ? 5 : bits == 6 ? 10 : 18;     // in quarters of a 4-bit step
     int best_ks = 1;
     long long best_cost = -1;
     for (int ks = 1; ks <= warps && ks <= nblk && ks <= 16; ks *= 2) {
@@ -116,7 +117,9 @@ size_t qmv_pipe_plan(int bits, const MmaParams& p, int tokens, int sms, PipePlan
         }
         const int n_groups = warps / ks;
         const long long rounds = (cta_blocks + n_groups - 1) / n_groups;
-        const long long cost = rounds * (slice + 3);        // (measured: ending a block and meeting the group costs about three steps)
+        // (measured: ending a block and meeting the group costs about as much as three 4-bit steps; a step of the
+        // widths whose codes straddle bytes costs several times a 4-bit one in unpacking)
+        const long long cost = rounds * (static_cast<long long>(slice) * step_weight + 12);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_ks = ks; }
     }
     pp.ks = best_ks;
@@ -171,7 +174,12 @@ size_t qmv_pipe_plan(int bits, const MmaParams& p, int tokens, int sms, PipePlan
         const int a = ((nblk * kw) >> pp.ks_shift) << p.spg_shift, b = ((nblk * (kw + 1)) >> pp.ks_shift) << p.spg_shift;
         if ((b - a) % 2 != 0) pp.unroll = 1;
     }
-    const long long total = static_cast<long long>(pp.off_ring) + static_cast<long long>(warps) * PIPE_DEPTH * slot_bytes;
+    pp.depth = PIPE_DEPTH;
+    long long total = static_cast<long long>(pp.off_ring) + static_cast<long long>(warps) * pp.depth * slot_bytes;
+    if (total > SMEM_WHOLE && !pp.special) {
+        pp.depth = 2;
+        total = static_cast<long long>(pp.off_ring) + static_cast<long long>(warps) * pp.depth * slot_bytes;
+    }
     return total <= SMEM_WHOLE ? static_cast<size_t>(total) : 0;
 }
 

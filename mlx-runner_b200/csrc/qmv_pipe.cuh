@@ -27,6 +27,7 @@ namespace mlxq {
 
 struct PipePlan {
     int ks, ks_shift;    // warps that share a block along K (1, 2, 4, 8 or 16) and its log2
+    int depth;           // ring slots per warp: PIPE_DEPTH, or 2 when the full ring does not fit
     int unroll;          // steps per turn of the main loop: 2 when every warp's slice holds an even number of steps, else 1
     int grid;
     int n_blocks;        // 16-row blocks; CTA b walks base_blocks (+ 1 if b < extra_blocks) of them
@@ -187,7 +188,8 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     constexpr bool LAST_ONLY = SP && SP_SPC % UNR == 0;
     constexpr bool SAME_AB = SP && CL <= GS;
     constexpr int NT = PIPE_WARPS * 32;
-    constexpr int DEPTH = PIPE_DEPTH;
+    // ring slots per warp: PIPE_DEPTH, or two where the larger ring does not fit beside many tokens' activations
+    const int depth = SP ? PIPE_DEPTH : pp.depth;
     constexpr uint32_t SB_OFF = 2 * 32 * LB;                   // (scale, bias) pairs follow the weights in a slot
     constexpr uint32_t SLOT = SB_OFF + 4 * 32 * 4;
     extern __shared__ __align__(128) uint8_t smem_pipe[];
@@ -228,8 +230,8 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     const int gmin = (s_begin * KB) >> gs_shift;
     float* scr = reinterpret_cast<float*>(smem_pipe + pp.off_scratch + static_cast<size_t>(warp) * pp.scratch_bytes);
     // the warp's ring, addressed through the lane's own cell: 16 (or 8) bytes inside every row of cells of a slot
-    const uint32_t ring = smem_u32(smem_pipe + pp.off_ring) + warp * (DEPTH * SLOT) + (LB == 16 ? lane * 16 : lane * 8);
-    const uint32_t ring_end = ring + DEPTH * SLOT;
+    const uint32_t ring = smem_u32(smem_pipe + pp.off_ring) + warp * (depth * SLOT) + (LB == 16 ? lane * 16 : lane * 8);
+    const uint32_t ring_end = ring + depth * SLOT;
     const uint32_t sb_delta = SB_OFF + lane * 4 - (LB == 16 ? lane * 16 : lane * 8);    // from there to the lane's first pair cell
     const uint32_t zaddr0 = smem_u32(smem_pipe + pp.off_zero);
 
@@ -267,7 +269,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         return r;
     };
 
-    // ---- the copy stream: this warp's (block, step) pairs in order, DEPTH of them in flight ------------------------
+    // ---- the copy stream: this warp's (block, step) pairs in order, `depth` of them in flight ------------------------
     // block j of the CTA is blockIdx.x + j * gridDim.x; group gi takes j = gi, gi + n_groups, ...
     const int cta_blocks = pp.base_blocks + (static_cast<int>(blockIdx.x) < pp.extra_blocks ? 1 : 0);
     const int my_blocks = cta_blocks > gi ? (cta_blocks - 1 - gi) / n_groups + 1 : 0;
@@ -342,7 +344,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     };
     if (l_left > 0) load_rows(l_blk);
 #pragma unroll
-    for (int gq = 0; gq < DEPTH / UNR; gq++) issue_turn(ring + gq * (UNR * SLOT));
+    for (int gq = 0; gq < depth / UNR; gq++) issue_turn(ring + gq * (UNR * SLOT));
 
     // ---- the activations: nothing before this line reads x, e or writes y --------------------------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -450,7 +452,8 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         uint32_t koff2 = s_begin * (KB * 2);                    // byte offset of the step's codes inside a staged column
         for (int s0 = s_begin; s0 < s_end; s0 += UNR, koff2 += UNR * KB * 2) {
             // the turn's UNR steps have landed: their words (and, for steps that close a drain cycle, the pairs) to registers
-            asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH / UNR - 1) : "memory");
+            if (depth == PIPE_DEPTH) asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_DEPTH / UNR - 1) : "memory");
+            else asm volatile("cp.async.wait_group %0;" ::"n"(2 / UNR - 1) : "memory");
             uint32_t w[UNR][2][NW];
             uint32_t sbv[UNR][4];                                // (read only where drains[i] holds)
             bool drains[UNR];
@@ -566,7 +569,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                     }
                 }
             });
-            // the turn's slots are in registers: refill them with the steps that are DEPTH ahead
+            // the turn's slots are in registers: refill them with the steps that are `depth` ahead
             issue_turn(c_src);
             c_src += UNR * SLOT;
             if (c_src == ring_end) c_src = ring;
