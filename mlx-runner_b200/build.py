@@ -32,6 +32,7 @@ UNITS = [("qmv_inst.cu", f"qmv_b{b}.o", [f"-DMLXQ_BITS={b}"]) for b in (2, 3, 4,
     ("aux_kernels.cu", "aux_kernels.o", []),
     ("qmv_mma.cu", "qmv_mma.o", []),
     ("qmv_pipe.cu", "qmv_pipe.o", []),
+    ("qmv_tok.cu", "qmv_tok.o", []),
     ("qgemm_sm100.cu", "qgemm_sm100.o", []),
     ("api.cu", "api.o", []),
     ("comm.cu", "comm.o", []),

@@ -17,6 +17,7 @@
 #include "qmv.cuh"
 #include "qmv_mma.cuh"
 #include "qmv_pipe.cuh"
+#include "qmv_tok.cuh"
 
 namespace mlxq {
 
@@ -240,8 +241,19 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         mp.err = device_error_word(parts[0]->device);
         // Preferred: the persistent kernel fed by asynchronous copies (MLXQ_DECODE=mma keeps the register-fed one).
         const char* mode = getenv("MLXQ_DECODE");
+        const bool persistent = !(mode && strcmp(mode, "mma") == 0) && mp.err;
+        if (persistent && T >= 2 && !(mode && strcmp(mode, "pipe") == 0)) {
+            // two or more tokens: the token-major kernel where it serves the call (MLXQ_DECODE=pipe keeps the other)
+            TokPlan tp;
+            const size_t tsmem = qmv_tok_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), tp);
+            if (tsmem) {
+                const cudaError_t err = launch_qmv_tok(parts[0]->bits, mp, tp, tsmem, parts[0]->device, st);
+                if (err != cudaSuccess) return cuda_fail(err, "qmv (token-major) launch");
+                return MLXQ_OK;
+            }
+        }
         PipePlan pp;
-        const size_t rsmem = (mode && strcmp(mode, "mma") == 0) || !mp.err ? 0 : qmv_pipe_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), pp);
+        const size_t rsmem = !persistent ? 0 : qmv_pipe_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), pp);
         if (peer && !rsmem) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
         cudaError_t err = rsmem ? launch_qmv_pipe(parts[0]->bits, mp, pp, rsmem, parts[0]->device, st)
                                 : launch_qmv_mma(parts[0]->bits, mp, smem, parts[0]->device, st);

@@ -60,7 +60,7 @@ int nccl_fail(ncclResult_t r, const char* what) {
 
 // The gather window: two buffers of `bytes` each (calls alternate between them, so a rank that runs ahead
 // never overwrites rows a slower rank's next kernels still read), mapped into every peer through CUDA IPC,
-// plus one flag word per rank and a CTA counter.
+// plus two flag words per rank (rows done, call started), a CTA counter and the count of completed calls.
 struct GatherWindow {
     char* local = nullptr;
     char* peer[mlxq::MAX_PEERS + 1] = {};        // by rank; [rank] == local
@@ -92,7 +92,7 @@ __global__ void gather_wait_kernel(const unsigned* my_flags, int rank, int nrank
     for (;;) {
         unsigned seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flags + p) : "memory");
-        if (static_cast<int>(seen - epoch) >= 0) return;
+        if (static_cast<int>(seen - epoch * 1024u) >= 0) return;        // (PEER_UNITS per completed call, see qmv_pipe.cuh)
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         if (t - t0 > 2000000000ull) { atomicOr(err, 2u | 8u); return; }     // ERR_WAIT_TIMEOUT | ERR_PEER_FLAG
     }
@@ -193,7 +193,7 @@ int mlxq_comm_window(mlxq_comm_t c, size_t bytes) {
     cudaError_t e = cudaSetDevice(c->device);
     if (e != cudaSuccess) return mlxq::cuda_fail(e, "cudaSetDevice");
     GatherWindow& w = c->win;
-    // flags: one word per rank, then the CTA counter
+    // flags: a "done" word per rank (words 0-7), a "started" word per rank (8-15), the CTA counter (32), completed calls (40)
     if ((e = cudaMalloc(&w.local, 2 * bytes)) != cudaSuccess) return mlxq::cuda_fail(e, "window allocation");
     if ((e = cudaMalloc(&w.flags, 256)) != cudaSuccess) { close_window(c); return mlxq::cuda_fail(e, "flag allocation"); }
     cudaMemset(w.local, 0, 2 * bytes);

@@ -16,8 +16,9 @@ struct PeerGather {
     char* y[MAX_PEERS];             // the local y pointer's twin inside each peer's window
     unsigned* flag[MAX_PEERS];      // each peer's flag array
     int peer_rank[MAX_PEERS];
-    unsigned* my_flags;             // this rank's flag array: slot r holds the last epoch rank r finished
-    unsigned* counter;              // CTAs of the running call that have stored all their rows (wraps at the grid size)
+    unsigned* my_flags;             // this rank's flag array: word r counts 1024 per call rank r has finished, word 8 + r is the
+                                    // number of the call rank r has started
+    unsigned* counter;              // CTAs of the running call that have published their rows (wraps at the grid size)
     int x_is_gathered;              // the activations lie in this rank's gather window (a previous call's output): wait for
                                     // the peers before reading them; otherwise the wait is put off until the first row is stored
     unsigned* epoch_ctr;            // device word holding the number of completed gather calls; when set, the kernel takes

@@ -20,6 +20,7 @@
 
 #include <type_traits>
 
+#include "code_plan.cuh"
 #include "qmv_mma.cuh"
 #include "sm100_ptx.cuh"
 
@@ -61,6 +62,39 @@ __device__ __forceinline__ void peer_flag_wait(const unsigned* flag, unsigned ep
     }
 }
 
+// The flag protocol of sharded calls.  Every rank owns slot r of two rows of words in every rank's flag array:
+// "done" -- PEER_UNITS per completed call, added piecemeal: every CTA adds its share once its rows are out, so no CTA
+// waits for another and the last store is followed by one release, not by a grid-wide count and a second fence --
+// and "started" -- the number of the call whose kernel has got past the point where everything enqueued before it is
+// complete (a peer may then overwrite the window buffer of the call before the previous one).
+constexpr unsigned PEER_UNITS = 1024;
+constexpr int PEER_STARTED = 8;            // word offset of the "started" row in a flag array
+
+// After griddepcontrol.wait: tell the peers this rank has started call `epoch` (one CTA; no ordering needed beyond
+// the grid dependency itself).
+__device__ __forceinline__ void peer_announce_start(const PeerGather& pg, unsigned epoch) {
+    if (blockIdx.x == 0 && threadIdx.x < static_cast<unsigned>(pg.n))
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(pg.flag[threadIdx.x] + PEER_STARTED + pg.rank), "r"(epoch) : "memory");
+}
+
+// End of a CTA of a sharded call: its rows are on their way to every peer's window.  After the barrier one lane per
+// peer adds the CTA's share of PEER_UNITS to this rank's "done" word there with release semantics at system scope
+// (cumulative over the stores the barrier ordered before it).  Nobody waits here: the next call on the communicator
+// (or mlxq_comm_wait) waits for the peers' words.  The CTA that arrives last at the local counter records the
+// call's number on the device for the next launch.
+__device__ __forceinline__ void peer_publish(const PeerGather& pg, unsigned epoch) {
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        if (threadIdx.x < static_cast<unsigned>(pg.n)) {
+            const unsigned grid = gridDim.x, i = blockIdx.x;
+            const unsigned share = ((i + 1u) * PEER_UNITS) / grid - (i * PEER_UNITS) / grid;
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(pg.flag[threadIdx.x] + pg.rank), "r"(share) : "memory");
+        }
+        if (threadIdx.x == 0 && pg.epoch_ctr != nullptr && atomicInc(pg.counter, gridDim.x - 1) == gridDim.x - 1)
+            *reinterpret_cast<volatile unsigned*>(pg.epoch_ctr) = epoch;
+    }
+}
+
 // Eight consecutive activations as fp32 through the coherent path (ld.global.cg).  The kernel may be resident
 // while the previous grid of the stream is still writing these values (dependent launch), and on sharded calls
 // peers write them over NVLink: the non-coherent read-only path is only defined for data that nobody writes
@@ -74,6 +108,36 @@ __device__ __forceinline__ void load8_coherent(const void* x, int dt, size_t ind
     }
     const uint4 v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + index));
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (dt == DT_F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            o[2 * i] = f.x; o[2 * i + 1] = f.y;
+        } else {
+            o[2 * i] = __uint_as_float(w[i] << 16);
+            o[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+}
+
+// The same in two halves, so that several chunks' loads can be in flight before the first is used: the raw 16 bytes
+// (16-bit types) or 32 bytes (fp32), then the conversion.
+__device__ __forceinline__ void load8_raw(const void* x, int dt, size_t index, uint4& a, uint4& b) {
+    if (dt == DT_F32) {
+        a = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(x) + index));
+        b = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(x) + index) + 1);
+    } else {
+        a = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + index));
+        b = a;
+    }
+}
+__device__ __forceinline__ void raw_to_float8(int dt, const uint4& a, const uint4& b, float (&o)[8]) {
+    if (dt == DT_F32) {
+        o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.y); o[2] = __uint_as_float(a.z); o[3] = __uint_as_float(a.w);
+        o[4] = __uint_as_float(b.x); o[5] = __uint_as_float(b.y); o[6] = __uint_as_float(b.z); o[7] = __uint_as_float(b.w);
+        return;
+    }
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         if (dt == DT_F16) {
@@ -163,6 +227,13 @@ __device__ __forceinline__ void stage8v_f16(__half* col, int k, const uint32_t (
         o = make_uint4(w[0], w[1], w[2], w[3]);
     }
     *reinterpret_cast<uint4*>(col + k) = o;
+}
+
+// staging of a chunk for a kernel whose lanes take runs of CL codes
+template <int BITS, int CL>
+__device__ __forceinline__ void stage8r(__half* col, int k, const float (&v)[8]) {
+    if constexpr (planned_width<BITS>()) stage8_plan<BITS, CL>(col, k, v);
+    else stage8v<BITS>(col, k, v);
 }
 
 constexpr int pipe_log2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
@@ -353,15 +424,16 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         // The call's number on the communicator: from the device-side count of completed calls when there is one (the
         // previous grid, which wrote it, is complete here), so that a launch captured in a graph stays correct on replay.
         if (q.peer.epoch_ctr != nullptr) peer_epoch = *reinterpret_cast<volatile unsigned*>(q.peer.epoch_ctr) + 1u;
+        peer_announce_start(q.peer, peer_epoch);
         if (peer_epoch != 1u && q.peer.x_is_gathered) {
             // the activations are the previous sharded call's gathered output: every peer must have finished it
-            if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
+            if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], (peer_epoch - 1u) * PEER_UNITS, p.err);
             __syncthreads();
         }
     }
-    // Otherwise the wait for the peers' previous call only guards their window buffers (this call's rows go where the
-    // rows of the call before the previous one were, which a peer may read until its previous call has run): it is
-    // put off until a warp stores its first rows, by when the peers' flags have usually arrived.
+    // Otherwise the peers only have to have STARTED their previous call (this call's rows go where the rows of the
+    // call before the previous one were, which a peer may read until its previous call runs): that wait is put off
+    // until a warp stores its first rows, and ranks in step never spend time in it.
     bool peers_ready = q.peer.n == 0 || q.peer.x_is_gathered || peer_epoch == 1u;
     {
         // staged once per CTA: fp16, permuted and pre-scaled to match the A registers (see qmv_mma.cuh), eight
@@ -373,7 +445,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             const int idx = base + threadIdx.x;
             const int tok = T == 1 ? 0 : pp.cpr_shift >= 0 ? idx >> pp.cpr_shift : idx / cpr, k = (idx - tok * cpr) * 8;
             float sum = 0.0f;
-            if (idx < total_chunks && BITS != 2 && split == 1 && q.x_dtype == DT_F16) {
+            if (idx < total_chunks && (BITS == 4 || BITS == 8) && split == 1 && q.x_dtype == DT_F16) {
                 // fp16 activations stay fp16: permute and pre-scale the words, the sum alone is formed in fp32
                 const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(q.x) + static_cast<size_t>(tok) * q.x_stride + k));
                 const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -383,20 +455,20 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                     sum += f.x;
                     sum += f.y;
                 }
-                if constexpr (BITS != 2) stage8v_f16<BITS>(xs + static_cast<size_t>(tok) * pp.xstride, k, w4);
+                if constexpr (BITS == 4 || BITS == 8) stage8v_f16<BITS>(xs + static_cast<size_t>(tok) * pp.xstride, k, w4);
             } else if (idx < total_chunks) {
                 float v[8];
                 load8_coherent(q.x, q.x_dtype, static_cast<size_t>(tok) * q.x_stride + k, v);
 #pragma unroll
                 for (int i = 0; i < 8; i++) sum += v[i];
                 if (split == 1) {
-                    stage8v<BITS>(xs + static_cast<size_t>(tok) * pp.xstride, k, v);
+                    stage8r<BITS, CL>(xs + static_cast<size_t>(tok) * pp.xstride, k, v);
                 } else {
                     float hi[8], lo[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) { hi[i] = __half2float(__float2half_rn(v[i])); lo[i] = v[i] - hi[i]; }
-                    stage8v<BITS>(xs + static_cast<size_t>(2 * tok) * pp.xstride, k, hi);
-                    stage8v<BITS>(xs + static_cast<size_t>(2 * tok + 1) * pp.xstride, k, lo);
+                    stage8r<BITS, CL>(xs + static_cast<size_t>(2 * tok) * pp.xstride, k, hi);
+                    stage8r<BITS, CL>(xs + static_cast<size_t>(2 * tok + 1) * pp.xstride, k, lo);
                 }
             }
             for (int o = 1; o < cpg; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -499,10 +571,10 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                 static_for<0, NM, 2>([&](auto jc) {
                     constexpr int j = decltype(jc)::value;
                     uint32_t a00, a01, a02, a03, a10, a11, a12, a13;
-                    a_regs<BITS>(w[i][0], j, a00, a02);
-                    a_regs<BITS>(w[i][1], j, a01, a03);
-                    a_regs<BITS>(w[i][0], j + 1, a10, a12);
-                    a_regs<BITS>(w[i][1], j + 1, a11, a13);
+                    a_regs_run<BITS, CL, j>(w[i][0], a00, a02);
+                    a_regs_run<BITS, CL, j>(w[i][1], a01, a03);
+                    a_regs_run<BITS, CL, j + 1>(w[i][0], a10, a12);
+                    a_regs_run<BITS, CL, j + 1>(w[i][1], a11, a13);
 #pragma unroll
                     for (int ps = 0; ps < NP; ps++) {
                         // (not volatile: the staged activations do not change after the barrier that follows the staging,
@@ -616,7 +688,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         else __syncwarp();
         if (kw == 0) {
             if (!peers_ready) {
-                if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
+                if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + PEER_STARTED + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
                 __syncwarp();
                 peers_ready = true;
             }
@@ -643,25 +715,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    if (q.peer.n > 0) {
-        // Sharded call: this CTA's rows are on their way to every peer's window.  The CTA that finishes last
-        // publishes this rank's epoch in every peer's flag array.  Nobody waits here: the next call on the
-        // communicator (or mlxq_comm_wait) waits for the peers' flags before it reads the gathered rows,
-        // and by then its own weight copies are already in flight.
-        if (kw == 0) __threadfence_system();                    // (only a group's first warp stored rows)
-        __syncthreads();
-        if (warp == 0) {
-            unsigned fin = 0;
-            if (lane == 0) fin = atomicInc(q.peer.counter, gridDim.x - 1) == gridDim.x - 1 ? 1u : 0u;
-            fin = __shfl_sync(0xffffffffu, fin, 0);
-            if (fin) {
-                __threadfence_system();
-                if (lane < q.peer.n)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(q.peer.flag[lane] + q.peer.rank), "r"(peer_epoch) : "memory");
-                if (lane == 0 && q.peer.epoch_ctr != nullptr) *reinterpret_cast<volatile unsigned*>(q.peer.epoch_ctr) = peer_epoch;
-            }
-        }
-    }
+    if (q.peer.n > 0) peer_publish(q.peer, peer_epoch);
 }
 
 // Plans the launch and the shared-memory layout for a call; returns the bytes needed, 0 when the call does not fit.

@@ -161,6 +161,25 @@ def test_small_batch_fused_with_bias_matches_separate(mlxq, oracle):
 
 
 @pytest.mark.parametrize("bits", [2, 3, 4, 5, 6, 8])
+def test_small_batches_every_width_and_group(mlxq, oracle, bits):
+    # Two to sixteen tokens take the decode kernel whose accumulator columns are tokens (where it serves the width and
+    # group size; the others fall to the general kernels): both 16-bit scale types, fp16 and fp32 activations, a row
+    # count that ends inside a block, group counts that leave windows of eight groups partly empty.  The bar is the
+    # fp32 reassociation noise of a K-long sum, far below the 1e-3 of the reference's own tests.
+    K, O = 1536, 72
+    for gs in (32, 64, 128):
+        for st in (oracle.F16, oracle.BF16):
+            fx = oracle.QuantFixture(O=O, K=K, bits=bits, gs=gs, scale_type=st, with_bias=(gs == 64), seed=bits * 7 + gs)
+            layer = DevLayer.from_fixture(mlxq, fx)
+            for T, x_dtype in ((2, 1), (5, 1), (8, 1), (9, 1), (16, 1), (3, 0), (8, 0), (4, 2)):
+                x = oracle.RNG(T * 17 + gs + bits).floats(T * K).reshape(T, K)
+                xr = as_dtype(x, x_dtype).float().cpu().numpy()
+                got = run(layer, x, T, x_dtype=x_dtype, x_stride=K + 8, y_stride=O + 5)
+                # (fp32 activations ride as two fp16 columns: the split leaves 2^-22 of every product)
+                close(oracle, got, fx.reference(xr), f"bits {bits} gs {gs} st {st} T {T} x {x_dtype}", 1e-4 if x_dtype == 0 else 3e-5)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 6, 8])
 def test_quantized_embedding_lookup(mlxq, oracle, bits):
     # KernelTests.swift:287-296 (4-bit there; every width here)
     K, V = 128, 16
