@@ -261,6 +261,8 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     constexpr int NT = PIPE_WARPS * 32;
     // ring slots per warp: PIPE_DEPTH, or two where the larger ring does not fit beside many tokens' activations
     const int depth = SP ? PIPE_DEPTH : pp.depth;
+    constexpr int RB = 4 * LB;                                 // bytes of a row per step
+    constexpr int PPR = RB / 16, NPT = RB / 32;                // 16-byte pieces per row; pieces per lane (16 rows)
     constexpr uint32_t SB_OFF = 2 * 32 * LB;                   // (scale, bias) pairs follow the weights in a slot
     constexpr uint32_t SLOT = SB_OFF + 4 * 32 * 4;
     extern __shared__ __align__(128) uint8_t smem_pipe[];
@@ -301,9 +303,14 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     const int gmin = (s_begin * KB) >> gs_shift;
     float* scr = reinterpret_cast<float*>(smem_pipe + pp.off_scratch + static_cast<size_t>(warp) * pp.scratch_bytes);
     // the warp's ring, addressed through the lane's own cell: 16 (or 8) bytes inside every row of cells of a slot
-    const uint32_t ring = smem_u32(smem_pipe + pp.off_ring) + warp * (depth * SLOT) + (LB == 16 ? lane * 16 : lane * 8);
+    // A step's bytes of the warp's sixteen rows lie row after row in a slot (RB bytes each); the warp copies them as
+    // 16-byte pieces, lane l the pieces l, l + 32, ..., so that every copy instruction reads whole 32-byte sectors.
+    // At 2, 4 and 8 bits a lane's pieces are exactly the bytes it consumes (rows g and g + 8, 16 bytes at 16 t); at
+    // the other widths it consumes 24 or 40 bytes at LB * t of those rows, which other lanes copied.
+    const uint32_t ring = smem_u32(smem_pipe + pp.off_ring) + warp * (depth * SLOT) + lane * 16;
     const uint32_t ring_end = ring + depth * SLOT;
-    const uint32_t sb_delta = SB_OFF + lane * 4 - (LB == 16 ? lane * 16 : lane * 8);    // from there to the lane's first pair cell
+    const uint32_t sb_delta = SB_OFF + lane * 4 - lane * 16;   // from there to the lane's first pair cell
+    const uint32_t rd_delta = LB == 16 ? 0u : static_cast<uint32_t>(g * RB + t * LB - lane * 16);   // ... and to the bytes it consumes
     const uint32_t zaddr0 = smem_u32(smem_pipe + pp.off_zero);
 
     const int run_grp_a = ((t * CL + mma_code_offset<BITS>(0)) >> gs_shift) & (G - 1);
@@ -347,15 +354,27 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     const int blk_stride = n_groups * gridDim.x;
     int l_left = my_blocks * nsteps;                           // steps not yet issued
     int l_s = s_begin, l_blk = blockIdx.x + gi * gridDim.x;
-    const uint8_t* l_w[2] = {nullptr, nullptr};                // the two rows at the cursor's step
+    const uint8_t* l_w[NPT];                                   // the lane's pieces at the cursor's step
     const char* l_sp[2] = {nullptr, nullptr};
     const char* l_bp[2] = {nullptr, nullptr};
+#pragma unroll
+    for (int m = 0; m < NPT; m++) l_w[m] = nullptr;
     auto load_rows = [&](int blk) {
+#pragma unroll
+        for (int m = 0; m < NPT; m++) {
+            // piece lane + 32 m of the block's step: row (of sixteen) and 16-byte part of that row
+            const int pc = lane + 32 * m, rr = pc / PPR, part16 = pc - rr * PPR;
+            int r = min(blk * 16 + rr, q.total_rows - 1), pi = 0;
+            if (q.n_parts > 1 && r >= q.part[0].rows) {
+                r -= q.part[0].rows; pi = 1;
+                if (q.n_parts > 2 && r >= q.part[1].rows) { r -= q.part[1].rows; pi = 2; }
+            }
+            l_w[m] = q.part[pi].w + static_cast<size_t>(r) * row_bytes + part16 * 16 + static_cast<size_t>(s_begin) * RB;
+        }
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             int pi;
             const int r = locate(blk, h, pi);
-            l_w[h] = q.part[pi].w + static_cast<size_t>(r) * row_bytes + t * LB + static_cast<size_t>(s_begin) * (4 * LB);
             if (async_sb) {
                 const size_t off = static_cast<size_t>(r) * groups * sbytes;
                 l_sp[h] = static_cast<const char*>(q.part[pi].s) + off;
@@ -371,17 +390,10 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         if (l_left > 0) {
             static_for<0, UNR, 1>([&](auto ic) {
                 constexpr int i = decltype(ic)::value;
-                if constexpr (LB == 16) {
-                    cp_async16<i * SLOT, i * 4 * LB>(dst, l_w[0]);
-                    cp_async16<i * SLOT + 512, i * 4 * LB>(dst, l_w[1]);
-                } else {
-                    // 24 or 40 bytes per lane as 8-byte pieces; piece k of all lanes forms one 256-byte row of cells
-                    static_for<0, LB / 8, 1>([&](auto kc) {
-                        constexpr int k = decltype(kc)::value;
-                        cp_async8<i * SLOT + k * 256, i * 4 * LB + 8 * k>(dst, l_w[0]);
-                        cp_async8<i * SLOT + (LB / 8 + k) * 256, i * 4 * LB + 8 * k>(dst, l_w[1]);
-                    });
-                }
+                static_for<0, NPT, 1>([&](auto mc) {
+                    constexpr int m = decltype(mc)::value;
+                    cp_async16<i * SLOT + m * 512, i * RB>(dst, l_w[m]);
+                });
                 const int ls = l_s + i;
                 if (async_sb && (!LAST_ONLY || i == UNR - 1) && ((((ls + 1) & dmask) == 0) || (!SP && ls + 1 == s_end))) {
                     // the step closes a drain cycle: the pair (g0, g0 + 1) is fetched when either group lies inside this
@@ -397,13 +409,15 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                 }
             });
             l_left -= UNR; l_s += UNR;
-            l_w[0] += UNR * 4 * LB; l_w[1] += UNR * 4 * LB;
+#pragma unroll
+            for (int m = 0; m < NPT; m++) l_w[m] += UNR * RB;
             if (l_s == s_end) {
                 l_s = s_begin; l_blk += blk_stride;
                 if (l_left > 0) {
                     if (q.n_parts == 1 && l_blk * 16 + 16 <= q.total_rows) {
                         // one part, a whole block inside the layer: the next block's rows are a constant distance on
-                        l_w[0] += w_jump; l_w[1] += w_jump;
+#pragma unroll
+                        for (int m = 0; m < NPT; m++) l_w[m] += w_jump;
                         if (async_sb) { l_sp[0] += s_jump; l_sp[1] += s_jump; l_bp[0] += s_jump; l_bp[1] += s_jump; }
                     } else {
                         load_rows(l_blk);
@@ -526,6 +540,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             // the turn's UNR steps have landed: their words (and, for steps that close a drain cycle, the pairs) to registers
             if (depth == PIPE_DEPTH) asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_DEPTH / UNR - 1) : "memory");
             else asm volatile("cp.async.wait_group %0;" ::"n"(2 / UNR - 1) : "memory");
+            if constexpr (LB != 16) __syncwarp();               // (the bytes a lane consumes were copied by other lanes)
             uint32_t w[UNR][2][NW];
             uint32_t sbv[UNR][4];                                // (read only where drains[i] holds)
             bool drains[UNR];
@@ -540,9 +555,9 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                     static_for<0, LB / 8, 1>([&](auto kc) {
                         constexpr int k = decltype(kc)::value;
                         asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];"
-                                     : "=r"(w[i][0][2 * k]), "=r"(w[i][0][2 * k + 1]) : "r"(c_src), "n"(i * SLOT + k * 256));
+                                     : "=r"(w[i][0][2 * k]), "=r"(w[i][0][2 * k + 1]) : "r"(c_src + rd_delta), "n"(i * SLOT + 8 * k));
                         asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];"
-                                     : "=r"(w[i][1][2 * k]), "=r"(w[i][1][2 * k + 1]) : "r"(c_src), "n"(i * SLOT + (LB / 8 + k) * 256));
+                                     : "=r"(w[i][1][2 * k]), "=r"(w[i][1][2 * k + 1]) : "r"(c_src + rd_delta), "n"(i * SLOT + 8 * RB + 8 * k));
                     });
                 }
                 const int s = s0 + i;
@@ -642,6 +657,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
                 }
             });
             // the turn's slots are in registers: refill them with the steps that are `depth` ahead
+            if constexpr (LB != 16) __syncwarp();               // (... in every lane's registers)
             issue_turn(c_src);
             c_src += UNR * SLOT;
             if (c_src == ring_end) c_src = ring;

@@ -112,8 +112,14 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     // this warp's place: group `gi` of warps in the CTA, slice `kw` of K
     const int ks = tp.ks, gi = warp >> tp.ks_shift, kw = warp & (ks - 1), n_groups = TOK_WARPS >> tp.ks_shift;
     const int gmin = kw * slice_groups;                        // first quantisation group of the slice
-    const uint32_t ring = smem_u32(smem_tok + tp.off_ring) + warp * (depth * SLOT) + lane * PS;
+    // A group's bytes of the warp's sixteen rows lie row after row in a slot (RB bytes each); the warp copies them as
+    // 16-byte pieces, lane l the pieces l, l + 32, ... below NPIECE, so that the copies read whole sectors whatever
+    // the width; a lane then consumes GB bytes at GB * t of rows g and g + 8, which other lanes may have copied.
+    constexpr int RB = 4 * GB, PPR = RB / 16, NPIECE = RB, NPT = (NPIECE + 31) / 32;
+    constexpr bool OWN_BYTES = GB == 16;                       // the lane's pieces are exactly the bytes it consumes
+    const uint32_t ring = smem_u32(smem_tok + tp.off_ring) + warp * (depth * SLOT) + lane * 16;
     const uint32_t ring_end = ring + depth * SLOT;
+    const uint32_t rd_delta = static_cast<uint32_t>(g * RB + t * GB - lane * 16);
     const uint32_t tab = smem_u32(smem_tok + tp.off_tab) + warp * (ntab * nwin * 512) + lane * 16;
     const uint32_t zaddr0 = smem_u32(smem_tok + tp.off_zero);
     // The lane's (scale, bias) cells start as zeros and the copies only ever fill the pairs inside the slice, so a
@@ -136,21 +142,33 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     const int blk_stride = n_groups * gridDim.x;
     int l_left = my_blocks * slice_groups;                     // groups not yet issued
     int l_g = 0, l_blk = blockIdx.x + gi * gridDim.x, l_tab = 0;
-    const uint8_t* l_w[2] = {nullptr, nullptr};                // the lane's bytes of the two rows at the cursor's group
+    const uint8_t* l_w[NPT];                                   // the lane's pieces at the cursor's group
+#pragma unroll
+    for (int m = 0; m < NPT; m++) l_w[m] = nullptr;
     const char* l_sp[2] = {nullptr, nullptr};                  // scales / biases of the two rows, at the slice's first group
     const char* l_bp[2] = {nullptr, nullptr};
     auto load_rows = [&](int blk) {
 #pragma unroll
+        for (int m = 0; m < NPT; m++) {
+            // piece lane + 32 m of the block's group: row (of sixteen) and 16-byte part of that row
+            const int pc = min(lane + 32 * m, NPIECE - 1), rr = pc / PPR, part16 = pc - rr * PPR;
+            int r = min(blk * 16 + rr, q.total_rows - 1), pi = 0;
+            if (q.n_parts > 1 && r >= q.part[0].rows) {
+                r -= q.part[0].rows; pi = 1;
+                if (q.n_parts > 2 && r >= q.part[1].rows) { r -= q.part[1].rows; pi = 2; }
+            }
+            l_w[m] = q.part[pi].w + static_cast<size_t>(r) * row_bytes + static_cast<size_t>(gmin) * RB + part16 * 16;
+        }
+#pragma unroll
         for (int h = 0; h < 2; h++) {
             int pi;
             const int r = locate(blk, h, pi);
-            l_w[h] = q.part[pi].w + static_cast<size_t>(r) * row_bytes + static_cast<size_t>(gmin) * (4 * GB) + t * GB;
             const size_t off = (static_cast<size_t>(r) * groups + gmin) * 2;
             l_sp[h] = static_cast<const char*>(q.part[pi].s) + off;
             l_bp[h] = static_cast<const char*>(q.part[pi].b) + off;
         }
     };
-    const long long w_jump = static_cast<long long>(blk_stride) * 16 * static_cast<long long>(row_bytes) - static_cast<long long>(slice_groups) * (4 * GB);
+    const long long w_jump = static_cast<long long>(blk_stride) * 16 * static_cast<long long>(row_bytes) - static_cast<long long>(slice_groups) * RB;
     const long long s_jump = static_cast<long long>(blk_stride) * 16 * groups * 2;
     auto issue_turn = [&](uint32_t dst) {
         if (l_left > 0) {
@@ -168,19 +186,20 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
                     }
                 }
             }
-            static_for<0, NPC, 1>([&](auto pc_) {
-                constexpr int pc = decltype(pc_)::value;
-                cp_async_piece<PS, pc * 32 * PS, pc * PS>(dst, l_w[0]);
-                cp_async_piece<PS, (NPC + pc) * 32 * PS, pc * PS>(dst, l_w[1]);
+            static_for<0, NPT, 1>([&](auto mc) {
+                constexpr int m = decltype(mc)::value;
+                if (NPIECE % 32 == 0 || m + 1 < NPT || lane + 32 * m < NPIECE) cp_async16<m * 512, 0>(dst, l_w[m]);
             });
             l_left--; l_g++;
-            l_w[0] += 4 * GB; l_w[1] += 4 * GB;
+#pragma unroll
+            for (int m = 0; m < NPT; m++) l_w[m] += RB;
             if (l_g == slice_groups) {
                 l_g = 0; l_blk += blk_stride;
                 if (++l_tab == ntab) l_tab = 0;
                 if (l_left > 0) {
                     if (q.n_parts == 1 && l_blk * 16 + 16 <= q.total_rows) {
-                        l_w[0] += w_jump; l_w[1] += w_jump;
+#pragma unroll
+                        for (int m = 0; m < NPT; m++) l_w[m] += w_jump;
                         l_sp[0] += s_jump; l_sp[1] += s_jump; l_bp[0] += s_jump; l_bp[1] += s_jump;
                     } else {
                         load_rows(l_blk);
@@ -318,6 +337,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
             if (depth == 8) asm volatile("cp.async.wait_group 7;" ::: "memory");
             else if (depth == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
             else asm volatile("cp.async.wait_group 1;" ::: "memory");
+            if constexpr (!OWN_BYTES) __syncwarp();             // (the bytes a lane consumes were copied by other lanes)
             if (gw == 0) {
                 // the window's pairs (they arrived with the block's first group, at the latest)
                 uint32_t s0, s1, b0, b1;
@@ -347,17 +367,18 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
                 constexpr int pc = decltype(pc_)::value;
                 static_for<0, 2, 1>([&](auto hc) {
                     constexpr int h = decltype(hc)::value;
-                    constexpr int off = (h * NPC + pc) * 32 * PS;
+                    constexpr int off = h * 8 * RB + pc * PS;
                     constexpr int wi = pc * (PS / 4);
                     if constexpr (PS == 16)
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]), "=r"(wd[h][wi + 2]), "=r"(wd[h][wi + 3]) : "r"(c_src), "n"(off));
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]), "=r"(wd[h][wi + 2]), "=r"(wd[h][wi + 3]) : "r"(c_src + rd_delta), "n"(off));
                     else if constexpr (PS == 8)
-                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]) : "r"(c_src), "n"(off));
+                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]) : "r"(c_src + rd_delta), "n"(off));
                     else
-                        asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(wd[h][wi]) : "r"(c_src), "n"(off));
+                        asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(wd[h][wi]) : "r"(c_src + rd_delta), "n"(off));
                 });
             });
             // the slot is in registers: refill it with the group that is `depth` ahead
+            if constexpr (!OWN_BYTES) __syncwarp();             // (... in every lane's registers)
             issue_turn(c_src);
             c_src += SLOT;
             if (c_src == ring_end) c_src = ring;
