@@ -92,11 +92,11 @@ def workload(args):
                             f"b4 g64, batch {args.batch}, fp16 x, fp32 y; {walks} walks per step ({per_walk / 1e9:.2f} GB per walk > L2)",
                 "layers": C4_LAYERS, "bits": 4, "group_size": 64, "batch": args.batch,
                 "launches_per_step": walks * C4_LAYERS * len(C4_PROJ), "l2": "inputs larger than L2"}, per_walk * walks
-    per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, 1)
+    per_launch = alg_bytes(O_ROWS, K_COLS, BITS, GS, args.batch)
     launches = args.layers * args.passes
-    return {"workload": f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M=1, fp16 x, fp32 y; {args.passes} passes over "
+    return {"workload": f"decode matvec {O_ROWS}x{K_COLS} b{BITS} g{GS} M={args.batch}, fp16 x, fp32 y; {args.passes} passes over "
                         f"{args.layers} distinct weight sets per step ({args.layers * per_launch / 1e6:.0f} MB > L2)",
-            "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS, "group_size": GS, "batch": 1,
+            "rows_per_gpu": O_ROWS, "in_dim": K_COLS, "bits": BITS, "group_size": GS, "batch": args.batch,
             "launches_per_step": launches, "l2": "inputs larger than L2"}, per_launch * launches
 
 
@@ -346,7 +346,7 @@ def run_ours(args):
     cfg, step_bytes = workload(args)
     fused = comm is not None and args.gather == "fused"
     strong = args.config != "default"
-    batch = args.batch if strong else 1
+    batch = args.batch
 
     # ---- the step's calls: (layer, activations, rows of the whole layer) in order ---------------------------------
     calls, keep = [], []
@@ -529,7 +529,7 @@ def run_ours(args):
         cfg = dict(cfg)
         cfg["launch"] = launch_mode
         cfg["parallelism"] = (f"row-shard x{world} + " + ("peer-store gather fused into the kernel" if fused else "ncclAllGather")) if world > 1 else "single GPU"
-        captured_shape = args.config == "default" and world == 1 and args.layers == LAYERS
+        captured_shape = args.config == "default" and world == 1 and args.layers == LAYERS and args.batch == 1
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
@@ -574,6 +574,8 @@ def run_sweep(args):
     peak = measured_peaks()["hbm_gbs"]
 
     def one(O, K, bits, gs, M, L=8, reps=10):
+        if O * K * bits // 8 > 200e6:
+            L = 2                                       # (two sets of a vocabulary-sized layer already exceed L2 several times)
         layers, keep = [], []
         for i in range(L):
             lay = synth.make_layer(O, K, bits, gs, synth.F16, seed=i, keep_codes=False)
@@ -611,8 +613,10 @@ def run_sweep(args):
     print("| shape (out x in) | bits | group | M | us per launch | GB/s | of measured peak |")
     print("|---|---|---|---|---|---|---|")
     cases = [(11008, 4096, b, 64, m) for b in (2, 3, 4, 5, 6, 8) for m in (1, 8)]
+    cases += [(11008, 4096, 4, 64, m) for m in (2, 4, 16)]
     cases += [(4096, 11008, 4, 64, m) for m in (1, 8)] + [(11008, 4096, 4, gs, m) for gs in (32, 128) for m in (1, 4)]
     cases += [(24576, 4096, 4, 64, 1), (6144, 4096, 4, 64, 1), (4096, 12288, 4, 64, 1), (4096, 4096, 4, 64, 1)]
+    cases += [(151936, 4096, b, 64, m) for b in (6, 8) for m in (1, 4, 16)]
     for O, K, bits, gs, M in cases:
         us, gbs = one(O, K, bits, gs, M)
         print(f"| {O} x {K} | {bits} | {gs} | {M} | {us:.1f} | {gbs:.0f} | {gbs / peak:.2f} |", flush=True)
@@ -627,7 +631,7 @@ def main():
     ap.add_argument("--config", default="default", choices=["default", "c4", "c5"],
                     help="default: the 11008x4096 sweep shape (weak scaling); c4: projection walk; c5: vocabulary head (strong scaling)")
     ap.add_argument("--bits", type=int, default=8, choices=[6, 8], help="c5: bit width of the head")
-    ap.add_argument("--batch", type=int, default=1, help="c4 / c5: tokens per call")
+    ap.add_argument("--batch", type=int, default=1, help="tokens per call (the headline is 1)")
     ap.add_argument("--calls", type=int, default=0, help="c4: walks per step, c5: calls per step (0 = default)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length (0 = skip)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM probe")

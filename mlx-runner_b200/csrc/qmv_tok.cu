@@ -104,14 +104,16 @@ size_t qmv_tok_plan(int bits, const MmaParams& p, int tokens, int sms, TokPlan& 
     int off = align_up(p.xn * tp.xstride * 2, 16);
     tp.off_parts = off; off += align_up(3 * p.xn * tp.gpad * 4, 16);
     tp.off_zero = off; off += PIPE_ZERO_BYTES;
-    tp.off_part = off; off += 2 * warps * 16 * tp.tp * 4;
-    tp.off_tab = align_up(off, 128);
+    tp.off_part = off;
+    const int off_fixed = off;
     // K split and ring depth: the split that leaves the longest-working warp the least to do, among those whose
     // slices are equal, even, and at least two groups long; the deepest ring that fits.
     const int cta_blocks = (tp.n_blocks + tp.grid - 1) / tp.grid;
     long long best_cost = -1;
     size_t best_total = 0;
+    for (int parities = 2; parities >= 1 && best_cost < 0; parities--)
     for (int ks = 1; ks <= warps; ks *= 2) {
+        const int off_tab = align_up(off_fixed + parities * warps * 16 * tp.tp * 4, 128);
         if (groups % ks != 0) break;
         const int slice = groups / ks;
         if (slice % 2 != 0 || slice < 2) break;
@@ -122,7 +124,7 @@ size_t qmv_tok_plan(int bits, const MmaParams& p, int tokens, int sms, TokPlan& 
         const int nwin = (slice + 7) / 8;
         for (int depth = gb >= 16 ? 4 : 8; depth >= 2; depth /= 2) {
             const int ntab = depth / slice + 2;
-            const long long total = static_cast<long long>(tp.off_tab) + static_cast<long long>(warps) * ntab * nwin * 512;
+            const long long total = static_cast<long long>(off_tab) + static_cast<long long>(warps) * ntab * nwin * 512;
             const long long ring_at = (total + 127) / 128 * 128;
             const long long end = ring_at + static_cast<long long>(warps) * depth * slot_bytes;
             if (end > SMEM_WHOLE) continue;
@@ -131,7 +133,7 @@ size_t qmv_tok_plan(int bits, const MmaParams& p, int tokens, int sms, TokPlan& 
             if (best_cost < 0 || c < best_cost) {
                 best_cost = c; best_total = static_cast<size_t>(end);
                 tp.ks = ks; tp.depth = depth; tp.ntab = ntab; tp.nwin = nwin; tp.slice_groups = slice;
-                tp.off_ring = static_cast<int>(ring_at);
+                tp.off_ring = static_cast<int>(ring_at); tp.off_tab = off_tab; tp.parities = parities;
             }
             break;
         }

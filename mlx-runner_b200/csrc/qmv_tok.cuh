@@ -36,7 +36,8 @@ struct TokPlan {
     int gpad;            // floats per staged column of a part of the group sums (groups + 8, the tail zero)
     int off_parts;       // [3][staged columns][gpad] floats: the TF32 parts of the activations' group sums
     int off_zero;        // PIPE_ZERO_BYTES of zeros (B fragments of idle columns)
-    int off_part;        // partial sums [groups of warps][2][ks][16 * tp] floats
+    int parities;        // partial-sum slots per group of warps: 2 (alternating by block), or 1 where shared memory is short
+    int off_part;        // partial sums [groups of warps][parities][ks][16 * tp] floats
     int off_tab;         // per warp: ntab x nwin cells of 32 lanes x 16 bytes
     int off_ring;        // per warp: depth slots of 2 rows x 32 lanes x group bytes
 };
@@ -313,7 +314,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
         asm volatile("" : "+r"(xb[ps]), "+r"(sb_[ps]) :: "memory");
     }
     const int par_floats = ks * 16 * TP;
-    float* part_g = part + gi * 2 * par_floats;
+    float* part_g = part + gi * tp.parities * par_floats;
     uint32_t c_src = ring;
     int c_tab = 0;
     int c_blk = blockIdx.x + gi * gridDim.x;
@@ -419,7 +420,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
         if (++c_tab == ntab) c_tab = 0;
 
         // ---- end of a block: this warp's partial sums [16 rows][tokens] to the group's first warp -------------------
-        float* slot_base = part_g + ((bj & 1) ? par_floats : 0);
+        float* slot_base = part_g + ((tp.parities == 2 && (bj & 1)) ? par_floats : 0);
         float* mine = slot_base + kw * (16 * TP);
 #pragma unroll
         for (int ps = 0; ps < NP; ps++) {
@@ -441,7 +442,8 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
         else __syncwarp();
         // Every warp of the group adds up and stores a share of the block's outputs: a token's sixteen rows per half
         // warp.  (The two parities of the partial-sum slot keep a warp that runs ahead from overwriting sums still
-        // being read: it meets the others at the next block's barrier before it writes this parity again.)
+        // being read: it meets the others at the next block's barrier before it writes this parity again.  With a
+        // single slot the group meets a second time, after the reads.)
         if (2 * kw < T) {
             if (!peers_ready) {
                 if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + PEER_STARTED + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
@@ -467,6 +469,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
                 }
             }
         }
+        if (tp.parities == 1 && ks > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(ks * 32) : "memory");
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
