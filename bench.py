@@ -471,8 +471,21 @@ def run_ours(args):
     ms_api = timed(step, max(3, args.steps // 4)) / max(3, args.steps // 4) if timed_step is not step else ms / args.steps
     ms_kernel_only = None
     if world > 1:
+        # the step without its gathers, launched the same way as the timed step (a replayed graph when that was one)
         n = max(3, args.steps // 4)
-        ms_kernel_only = timed(lambda: step(gather=False), n) / n
+        plain = lambda: step(gather=False)      # noqa: E731
+        if timed_step is not step:
+            try:
+                torch.cuda.synchronize()
+                graph_k = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph_k):
+                    step(gather=False)
+                graph_k.replay()
+                torch.cuda.synchronize()
+                plain = graph_k.replay
+            except Exception:       # noqa: BLE001
+                pass
+        ms_kernel_only = timed(plain, n) / n
     for _ in range(2):
         step_e2e()
     t_a = time.perf_counter()

@@ -221,7 +221,7 @@ MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_str
  * or after mlxq_comm_wait(c, stream), which enqueues that wait alone; any other reader needs the latter.
  * The rows may be read by work enqueued on `stream` before this rank's NEXT fused call on the communicator, and only
  * by such work: calls alternate between two buffers, and a peer that runs ahead starts storing its second-next
- * call's rows into this buffer as soon as this rank has published its next call.
+ * call's rows into this buffer as soon as this rank's next call has started.
  * Every rank must issue the same sequence of fused calls.  The calls may be captured into a CUDA graph and replayed
  * (the call's number is kept on the device); a captured sequence must then hold an even number of fused calls of the
  * communicator, so that the two buffers keep alternating from one replay to the next.  Only shapes the persistent decode kernel serves

@@ -255,6 +255,15 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         PipePlan pp;
         const size_t rsmem = !persistent ? 0 : qmv_pipe_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), pp);
         if (peer && !rsmem) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
+        if (persistent && !rsmem && T >= 4) {
+            // Too many staged activation columns for a CTA's shared memory (long rows): two calls of half the tokens,
+            // each on a persistent kernel, beat the register-fed kernel although the weights are read twice.
+            const int64_t h0 = T / 2;
+            const int rc = run_qmv(parts, n, st, x, x_dtype, x_stride, y, y_dtype, y_stride, h0, e, act, nullptr);
+            if (rc != MLXQ_OK) return rc;
+            return run_qmv(parts, n, st, static_cast<const char*>(x) + static_cast<size_t>(h0) * x_stride * dtype_size(x_dtype), x_dtype, x_stride,
+                           static_cast<char*>(y) + static_cast<size_t>(h0) * y_stride * dtype_size(y_dtype), y_dtype, y_stride, T - h0, e, act, nullptr);
+        }
         cudaError_t err = rsmem ? launch_qmv_pipe(parts[0]->bits, mp, pp, rsmem, parts[0]->device, st)
                                 : launch_qmv_mma(parts[0]->bits, mp, smem, parts[0]->device, st);
         if (err != cudaSuccess) return cuda_fail(err, "qmv (tensor-core) launch");
