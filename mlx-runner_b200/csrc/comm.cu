@@ -60,7 +60,7 @@ int nccl_fail(ncclResult_t r, const char* what) {
 
 // The gather window: two buffers of `bytes` each (calls alternate between them, so a rank that runs ahead
 // never overwrites rows a slower rank's next kernels still read), mapped into every peer through CUDA IPC,
-// plus two flag words per rank (rows done, call started), a CTA counter and the count of completed calls.
+// plus one flag word per rank (its calls whose rows are complete), a CTA counter and the count of completed calls.
 struct GatherWindow {
     char* local = nullptr;
     char* peer[mlxq::MAX_PEERS + 1] = {};        // by rank; [rank] == local
@@ -80,19 +80,28 @@ struct mlxq_comm {
 
 namespace {
 
-// One warp: lane p waits (bounded, two seconds) until peer p's flag in this rank's array has reached the number of
-// this rank's completed fused calls (read from the device, so that the launch can be replayed from a graph).
-__global__ void gather_wait_kernel(const unsigned* my_flags, int rank, int nranks, const unsigned* epoch_ctr, unsigned* err) {
+// The flag words of the other ranks' arrays (this rank's word in each), by rank.
+struct PeerFlags {
+    unsigned* flag[mlxq::MAX_PEERS + 1];
+};
+
+// One warp.  First lane p publishes this rank's completed fused calls in rank p's flag array (the calls' kernels do
+// not publish themselves: the next kernel of the communicator on the rank does, and after the last call that is this
+// one -- the grids that stored the rows are complete here, so one release store covers them).  Then lane p waits
+// (bounded, two seconds) until peer p's word in this rank's array has reached the same number.  The number is read
+// from the device, so that the launch can be replayed from a graph.
+__global__ void gather_wait_kernel(const unsigned* my_flags, PeerFlags peers, int rank, int nranks, const unsigned* epoch_ctr, unsigned* err) {
     const int p = threadIdx.x;
     if (p >= nranks || p == rank) return;
     const unsigned epoch = *reinterpret_cast<const volatile unsigned*>(epoch_ctr);
     if (epoch == 0u) return;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flag[p] + rank), "r"(epoch) : "memory");
     unsigned long long t0, t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (;;) {
         unsigned seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flags + p) : "memory");
-        if (static_cast<int>(seen - epoch * 1024u) >= 0) return;        // (PEER_UNITS per completed call, see qmv_pipe.cuh)
+        if (static_cast<int>(seen - epoch) >= 0) return;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         if (t - t0 > 2000000000ull) { atomicOr(err, 2u | 8u); return; }     // ERR_WAIT_TIMEOUT | ERR_PEER_FLAG
     }
@@ -193,7 +202,7 @@ int mlxq_comm_window(mlxq_comm_t c, size_t bytes) {
     cudaError_t e = cudaSetDevice(c->device);
     if (e != cudaSuccess) return mlxq::cuda_fail(e, "cudaSetDevice");
     GatherWindow& w = c->win;
-    // flags: a "done" word per rank (words 0-7), a "started" word per rank (8-15), the CTA counter (32), completed calls (40)
+    // flags: a word per rank (0-7), the CTA counter (32), completed calls (40)
     if ((e = cudaMalloc(&w.local, 2 * bytes)) != cudaSuccess) return mlxq::cuda_fail(e, "window allocation");
     if ((e = cudaMalloc(&w.flags, 256)) != cudaSuccess) { close_window(c); return mlxq::cuda_fail(e, "flag allocation"); }
     cudaMemset(w.local, 0, 2 * bytes);
@@ -282,7 +291,9 @@ int mlxq_comm_wait(mlxq_comm_t c, mlxq_stream_t stream) {
     if (e != cudaSuccess) return mlxq::cuda_fail(e, "cudaSetDevice");
     unsigned* err = mlxq::device_error_word(c->device);
     if (!err) return mlxq::fail(MLXQ_GPU_FAILURE, "no error word on device %d", c->device);
-    gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->win.flags, c->rank, c->size, c->win.epoch_ctr, err);
+    PeerFlags pf = {};
+    for (int p = 0; p < c->size && p <= mlxq::MAX_PEERS; p++) pf.flag[p] = c->win.peer_flags[p];
+    gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->win.flags, pf, c->rank, c->size, c->win.epoch_ctr, err);
     e = cudaGetLastError();
     return e == cudaSuccess ? MLXQ_OK : mlxq::cuda_fail(e, "gather wait launch");
 }

@@ -16,8 +16,8 @@ struct PeerGather {
     char* y[MAX_PEERS];             // the local y pointer's twin inside each peer's window
     unsigned* flag[MAX_PEERS];      // each peer's flag array
     int peer_rank[MAX_PEERS];
-    unsigned* my_flags;             // this rank's flag array: word r counts 1024 per call rank r has finished, word 8 + r is the
-                                    // number of the call rank r has started
+    unsigned* my_flags;             // this rank's flag array: word r is the number of rank r's calls whose rows are complete
+                                    // everywhere (published by the kernel that follows a call, so also: rank r has started call word + 1)
     unsigned* counter;              // CTAs of the running call that have published their rows (wraps at the grid size)
     int x_is_gathered;              // the activations lie in this rank's gather window (a previous call's output): wait for
                                     // the peers before reading them; otherwise the wait is put off until the first row is stored

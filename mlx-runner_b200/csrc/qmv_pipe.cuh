@@ -62,37 +62,24 @@ __device__ __forceinline__ void peer_flag_wait(const unsigned* flag, unsigned ep
     }
 }
 
-// The flag protocol of sharded calls.  Every rank owns slot r of two rows of words in every rank's flag array:
-// "done" -- PEER_UNITS per completed call, added piecemeal: every CTA adds its share once its rows are out, so no CTA
-// waits for another and the last store is followed by one release, not by a grid-wide count and a second fence --
-// and "started" -- the number of the call whose kernel has got past the point where everything enqueued before it is
-// complete (a peer may then overwrite the window buffer of the call before the previous one).
-constexpr unsigned PEER_UNITS = 1024;
-constexpr int PEER_STARTED = 8;            // word offset of the "started" row in a flag array
-
-// After griddepcontrol.wait: tell the peers this rank has started call `epoch` (one CTA; no ordering needed beyond
-// the grid dependency itself).
-__device__ __forceinline__ void peer_announce_start(const PeerGather& pg, unsigned epoch) {
+// The flag protocol of sharded calls.  Every rank owns word r of every rank's flag array and keeps in it the number of
+// its fused calls whose rows are complete and visible everywhere.  A call does not publish itself: its kernel ends
+// without any system-scope fence, and the NEXT kernel of the communicator on that rank (the next fused call, or the
+// wait kernel of mlxq_comm_wait) publishes it right after its own start -- by then the grid that stored the rows is
+// complete, so one release store by one thread covers all of them, and its latency overlaps the new kernel's work
+// instead of stretching the old kernel's tail.  Hence word r >= e - 1 also says that rank r has STARTED call e, i.e.
+// that everything it enqueued before call e (the readers of call e - 2's rows, whose buffer call e overwrites) is done.
+__device__ __forceinline__ void peer_publish_previous(const PeerGather& pg, unsigned epoch) {
     if (blockIdx.x == 0 && threadIdx.x < static_cast<unsigned>(pg.n))
-        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(pg.flag[threadIdx.x] + PEER_STARTED + pg.rank), "r"(epoch) : "memory");
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pg.flag[threadIdx.x] + pg.rank), "r"(epoch - 1u) : "memory");
 }
 
-// End of a CTA of a sharded call: its rows are on their way to every peer's window.  After the barrier one lane per
-// peer adds the CTA's share of PEER_UNITS to this rank's "done" word there with release semantics at system scope
-// (cumulative over the stores the barrier ordered before it).  Nobody waits here: the next call on the communicator
-// (or mlxq_comm_wait) waits for the peers' words.  The CTA that arrives last at the local counter records the
-// call's number on the device for the next launch.
-__device__ __forceinline__ void peer_publish(const PeerGather& pg, unsigned epoch) {
+// End of a sharded call's CTA: nothing crosses the link here.  The CTA that arrives last at the local counter records
+// the call's number on the device for the next launch (which reads it after the grid dependency).
+__device__ __forceinline__ void peer_finish(const PeerGather& pg, unsigned epoch) {
     __syncthreads();
-    if (threadIdx.x < 32) {
-        if (threadIdx.x < static_cast<unsigned>(pg.n)) {
-            const unsigned grid = gridDim.x, i = blockIdx.x;
-            const unsigned share = ((i + 1u) * PEER_UNITS) / grid - (i * PEER_UNITS) / grid;
-            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(pg.flag[threadIdx.x] + pg.rank), "r"(share) : "memory");
-        }
-        if (threadIdx.x == 0 && pg.epoch_ctr != nullptr && atomicInc(pg.counter, gridDim.x - 1) == gridDim.x - 1)
-            *reinterpret_cast<volatile unsigned*>(pg.epoch_ctr) = epoch;
-    }
+    if (threadIdx.x == 0 && pg.epoch_ctr != nullptr && atomicInc(pg.counter, gridDim.x - 1) == gridDim.x - 1)
+        *reinterpret_cast<volatile unsigned*>(pg.epoch_ctr) = epoch;
 }
 
 // Eight consecutive activations as fp32 through the coherent path (ld.global.cg).  The kernel may be resident
@@ -438,10 +425,10 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         // The call's number on the communicator: from the device-side count of completed calls when there is one (the
         // previous grid, which wrote it, is complete here), so that a launch captured in a graph stays correct on replay.
         if (q.peer.epoch_ctr != nullptr) peer_epoch = *reinterpret_cast<volatile unsigned*>(q.peer.epoch_ctr) + 1u;
-        peer_announce_start(q.peer, peer_epoch);
+        peer_publish_previous(q.peer, peer_epoch);
         if (peer_epoch != 1u && q.peer.x_is_gathered) {
             // the activations are the previous sharded call's gathered output: every peer must have finished it
-            if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], (peer_epoch - 1u) * PEER_UNITS, p.err);
+            if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
             __syncthreads();
         }
     }
@@ -704,7 +691,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
         else __syncwarp();
         if (kw == 0) {
             if (!peers_ready) {
-                if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + PEER_STARTED + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
+                if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 2u, p.err);
                 __syncwarp();
                 peers_ready = true;
             }
@@ -731,7 +718,7 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    if (q.peer.n > 0) peer_publish(q.peer, peer_epoch);
+    if (q.peer.n > 0) peer_finish(q.peer, peer_epoch);
 }
 
 // Plans the launch and the shared-memory layout for a call; returns the bytes needed, 0 when the call does not fit.

@@ -218,9 +218,9 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     unsigned peer_epoch = q.peer.epoch;
     if (q.peer.n > 0) {
         if (q.peer.epoch_ctr != nullptr) peer_epoch = *reinterpret_cast<volatile unsigned*>(q.peer.epoch_ctr) + 1u;
-        peer_announce_start(q.peer, peer_epoch);
+        peer_publish_previous(q.peer, peer_epoch);
         if (peer_epoch != 1u && q.peer.x_is_gathered) {
-            if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], (peer_epoch - 1u) * PEER_UNITS, p.err);
+            if (warp == 0 && lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
             __syncthreads();
         }
     }
@@ -446,7 +446,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
         // single slot the group meets a second time, after the reads.)
         if (2 * kw < T) {
             if (!peers_ready) {
-                if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + PEER_STARTED + q.peer.peer_rank[lane], peer_epoch - 1u, p.err);
+                if (lane < q.peer.n) peer_flag_wait(q.peer.my_flags + q.peer.peer_rank[lane], peer_epoch - 2u, p.err);
                 __syncwarp();
                 peers_ready = true;
             }
@@ -473,7 +473,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    if (q.peer.n > 0) peer_publish(q.peer, peer_epoch);
+    if (q.peer.n > 0) peer_finish(q.peer, peer_epoch);
 }
 
 // Plans a call of the token-major kernel; returns the shared memory it needs, 0 when the call is not one it serves.
