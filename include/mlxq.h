@@ -222,6 +222,9 @@ MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_str
  * The rows may be read by work enqueued on `stream` before this rank's NEXT fused call on the communicator, and only
  * by such work: calls alternate between two buffers, and a peer that runs ahead starts storing its second-next
  * call's rows into this buffer as soon as this rank's next call has started.
+ * A rank's rows are announced to the peers by the kernel that follows the call on the communicator (the rank's next
+ * fused call or its mlxq_comm_wait), not by the call itself: a rank must enqueue one of those before it blocks on its
+ * peers, or a peer whose next call reads these rows gives up after two seconds.
  * Every rank must issue the same sequence of fused calls.  The calls may be captured into a CUDA graph and replayed
  * (the call's number is kept on the device); a captured sequence must then hold an even number of fused calls of the
  * communicator, so that the two buffers keep alternating from one replay to the next.  Only shapes the persistent decode kernel serves

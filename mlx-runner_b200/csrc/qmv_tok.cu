@@ -19,7 +19,8 @@ bool pdl_enabled() {
 
 bool supported(int bits, int gs) {
     const int gb_bits = gs * bits;                  // bits of a group per row
-    if (gb_bits % 128 != 0) return false;           // four lanes, whole 32-bit words each
+    if (gb_bits % 64 != 0 || gb_bits < 128) return false;      // four lanes, whole half words each, at least four bytes
+    if (gb_bits % 128 != 0 && bits != 3 && bits != 5 && bits != 6) return false;
     const int nm = gs / 16;
     return nm >= 2 && nm % 2 == 0;
 }

@@ -43,14 +43,17 @@ struct TokPlan {
 };
 
 template <int BITS, int GS> struct TokUnit {
-    static constexpr int GB = GS * BITS / 32;                                   // bytes of one group per lane and row
-    static constexpr int PS = GB % 16 == 0 ? 16 : GB % 8 == 0 ? 8 : 4;          // bytes per asynchronous copy
-    static constexpr int NPC = GB / PS;                                         // copies per row
-    static constexpr int NW = GB / 4;                                           // 32-bit words per row
+    static constexpr int GB = GS * BITS / 32;                                   // bytes of one group per lane and row (4 ... 32, or 6 / 10)
+    static constexpr bool WORDS = GB % 4 == 0;                                  // the lane's run starts on a word of its row
+    static constexpr int PS = GB % 16 == 0 ? 16 : GB % 8 == 0 ? 8 : 4;          // bytes per shared load of the run
+    static constexpr int NPC = WORDS ? GB / PS : (GB + 2 + 3) / 4;              // loads per row (unaligned runs: the words that hold run + 16 bits)
+    static constexpr int NW = (GB + 3) / 4;                                     // 32-bit words of a run
     static constexpr int CL = GS / 4;                                           // codes per lane and group
     static constexpr int NM = CL / 4;                                           // MMAs per group
-    static constexpr bool SUPPORTED = (GS * BITS) % 128 == 0 && NM >= 2 && NM % 2 == 0;
-    static constexpr uint32_t SLOT = 2 * 32 * GB;
+    static constexpr int RB = 4 * GB;                                           // bytes of a row per group
+    static constexpr int PIECE = RB % 16 == 0 ? 16 : 8;                         // bytes per asynchronous copy
+    static constexpr bool SUPPORTED = (GS * BITS) % 64 == 0 && GB >= 4 && NM >= 2 && NM % 2 == 0 && (WORDS || planned_width<BITS>());
+    static constexpr uint32_t SLOT = 16 * RB;
 };
 
 template <int PS, int DOFF, int SOFF>
@@ -116,11 +119,14 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     // A group's bytes of the warp's sixteen rows lie row after row in a slot (RB bytes each); the warp copies them as
     // 16-byte pieces, lane l the pieces l, l + 32, ... below NPIECE, so that the copies read whole sectors whatever
     // the width; a lane then consumes GB bytes at GB * t of rows g and g + 8, which other lanes may have copied.
-    constexpr int RB = 4 * GB, PPR = RB / 16, NPIECE = RB, NPT = (NPIECE + 31) / 32;
+    // (Rows of 24 or 40 bytes per group -- 3- and 5-bit at group 64, 6-bit at group 32 -- go as 8-byte pieces, and a
+    // lane's 6- or 10-byte run then starts on a half word: it loads the words around it and shifts by 0 or 16 bits.)
+    constexpr int RB = U::RB, PIECE = U::PIECE, PPR = RB / PIECE, NPIECE = 16 * PPR, NPT = (NPIECE + 31) / 32;
     constexpr bool OWN_BYTES = GB == 16;                       // the lane's pieces are exactly the bytes it consumes
-    const uint32_t ring = smem_u32(smem_tok + tp.off_ring) + warp * (depth * SLOT) + lane * 16;
+    const uint32_t ring = smem_u32(smem_tok + tp.off_ring) + warp * (depth * SLOT) + lane * PIECE;
     const uint32_t ring_end = ring + depth * SLOT;
-    const uint32_t rd_delta = static_cast<uint32_t>(g * RB + t * GB - lane * 16);
+    const uint32_t rd_delta = static_cast<uint32_t>(g * RB + ((t * GB) & ~3) - lane * PIECE);
+    const uint32_t rd_shift = static_cast<uint32_t>(((t * GB) & 3) * 8);     // 0 or 16 (0 when the run starts on a word)
     const uint32_t tab = smem_u32(smem_tok + tp.off_tab) + warp * (ntab * nwin * 512) + lane * 16;
     const uint32_t zaddr0 = smem_u32(smem_tok + tp.off_zero);
     // The lane's (scale, bias) cells start as zeros and the copies only ever fill the pairs inside the slice, so a
@@ -158,7 +164,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
                 r -= q.part[0].rows; pi = 1;
                 if (q.n_parts > 2 && r >= q.part[1].rows) { r -= q.part[1].rows; pi = 2; }
             }
-            l_w[m] = q.part[pi].w + static_cast<size_t>(r) * row_bytes + static_cast<size_t>(gmin) * RB + part16 * 16;
+            l_w[m] = q.part[pi].w + static_cast<size_t>(r) * row_bytes + static_cast<size_t>(gmin) * RB + part16 * PIECE;
         }
 #pragma unroll
         for (int h = 0; h < 2; h++) {
@@ -189,7 +195,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
             }
             static_for<0, NPT, 1>([&](auto mc) {
                 constexpr int m = decltype(mc)::value;
-                if (NPIECE % 32 == 0 || m + 1 < NPT || lane + 32 * m < NPIECE) cp_async16<m * 512, 0>(dst, l_w[m]);
+                if (NPIECE % 32 == 0 || m + 1 < NPT || lane + 32 * m < NPIECE) cp_async_piece<PIECE, m * 32 * PIECE, 0>(dst, l_w[m]);
             });
             l_left--; l_g++;
 #pragma unroll
@@ -364,20 +370,35 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
                 }
             }
             uint32_t wd[2][NW];
-            static_for<0, NPC, 1>([&](auto pc_) {
-                constexpr int pc = decltype(pc_)::value;
+            if constexpr (U::WORDS) {
+                static_for<0, NPC, 1>([&](auto pc_) {
+                    constexpr int pc = decltype(pc_)::value;
+                    static_for<0, 2, 1>([&](auto hc) {
+                        constexpr int h = decltype(hc)::value;
+                        constexpr int off = h * 8 * RB + pc * PS;
+                        constexpr int wi = pc * (PS / 4);
+                        if constexpr (PS == 16)
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]), "=r"(wd[h][wi + 2]), "=r"(wd[h][wi + 3]) : "r"(c_src + rd_delta), "n"(off));
+                        else if constexpr (PS == 8)
+                            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]) : "r"(c_src + rd_delta), "n"(off));
+                        else
+                            asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(wd[h][wi]) : "r"(c_src + rd_delta), "n"(off));
+                    });
+                });
+            } else {
+                // the run starts on a half word: NPC words from the word below it, moved down by 0 or 16 bits
                 static_for<0, 2, 1>([&](auto hc) {
                     constexpr int h = decltype(hc)::value;
-                    constexpr int off = h * 8 * RB + pc * PS;
-                    constexpr int wi = pc * (PS / 4);
-                    if constexpr (PS == 16)
-                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]), "=r"(wd[h][wi + 2]), "=r"(wd[h][wi + 3]) : "r"(c_src + rd_delta), "n"(off));
-                    else if constexpr (PS == 8)
-                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(wd[h][wi]), "=r"(wd[h][wi + 1]) : "r"(c_src + rd_delta), "n"(off));
-                    else
-                        asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(wd[h][wi]) : "r"(c_src + rd_delta), "n"(off));
+                    uint32_t raw[NPC];
+                    static_for<0, NPC, 1>([&](auto pc_) {
+                        constexpr int pc = decltype(pc_)::value;
+                        asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(raw[pc]) : "r"(c_src + rd_delta), "n"(h * 8 * RB + pc * 4));
+                    });
+#pragma unroll
+                    for (int wi = 0; wi < NW; wi++)
+                        wd[h][wi] = wi + 1 < NPC ? __funnelshift_r(raw[wi], raw[wi + 1], rd_shift) : raw[wi] >> rd_shift;
                 });
-            });
+            }
             // the slot is in registers: refill it with the group that is `depth` ahead
             if constexpr (!OWN_BYTES) __syncwarp();             // (... in every lane's registers)
             issue_turn(c_src);
