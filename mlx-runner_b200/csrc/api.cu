@@ -206,7 +206,8 @@ static void fill_qmv(QmvParams& p, const mlxq_linear_t* parts, int n) {
 // The tensor-core decode kernel takes a call when the batch is small, the group size is 32/64/128, K is a
 // multiple of the kernel's step and the rows are aligned for vector loads.  MLXQ_DECODE=cuda forces the
 // CUDA-core kernel (which handles every shape).  Returns the shared memory needed, 0 when not eligible.
-static size_t mma_plan(const mlxq_linear_t* parts, int n, int x_dtype, int64_t T, MmaParams& mp) {
+static size_t mma_plan(const mlxq_linear_t* parts, int n, int x_dtype, int64_t T, MmaParams& mp, bool* planned = nullptr) {
+    if (planned) *planned = false;
     const mlxq_linear* f = parts[0];
     const char* mode = getenv("MLXQ_DECODE");
     if (mode && strcmp(mode, "cuda") == 0) return 0;
@@ -217,6 +218,7 @@ static size_t mma_plan(const mlxq_linear_t* parts, int n, int x_dtype, int64_t T
         if (!aligned16(parts[i]->w)) return 0;
     mp.split = x_dtype == MLXQ_F32 ? 2 : 1;
     if (!qmv_mma_plan(f->bits, static_cast<int>(f->in_dim), f->gs, static_cast<int>(T) * mp.split, mp)) return 0;
+    if (planned) *planned = true;       // (the column plan exists; the register-fed kernel may still not fit: 0)
     return qmv_mma_smem(static_cast<int>(f->in_dim), f->gs, static_cast<int>(T), mp);
 }
 
@@ -233,7 +235,9 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
     p.e = e;
     p.act = act;
     MmaParams mp;
-    if (const size_t smem = mma_plan(parts, n, x_dtype, T, mp)) {
+    bool planned = false;
+    const size_t smem = mma_plan(parts, n, x_dtype, T, mp, &planned);
+    if (planned) {
         p.T = static_cast<int>(T);
         p.x = x;
         p.y = y;
@@ -255,19 +259,35 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         PipePlan pp;
         const size_t rsmem = !persistent ? 0 : qmv_pipe_plan(parts[0]->bits, mp, static_cast<int>(T), device_sm_count(parts[0]->device), pp);
         if (peer && !rsmem) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
-        if (persistent && !rsmem && T >= 4) {
+        // does a call of `t` tokens run on one of the persistent kernels?
+        auto fits_persistent = [&](int64_t t) {
+            MmaParams m2;
+            bool ok2 = false;
+            mma_plan(parts, n, x_dtype, t, m2, &ok2);
+            if (!ok2) return false;
+            m2.q = p;
+            m2.q.T = static_cast<int>(t);
+            m2.err = mp.err;
+            TokPlan t2;
+            PipePlan p2;
+            const int sms = device_sm_count(parts[0]->device);
+            return (t >= 2 && qmv_tok_plan(parts[0]->bits, m2, static_cast<int>(t), sms, t2) != 0) || qmv_pipe_plan(parts[0]->bits, m2, static_cast<int>(t), sms, p2) != 0;
+        };
+        const int64_t h0 = T / 2;
+        if (persistent && !rsmem && T >= 4 && fits_persistent(h0) && fits_persistent(T - h0)) {
             // Too many staged activation columns for a CTA's shared memory (long rows): two calls of half the tokens,
             // each on a persistent kernel, beat the register-fed kernel although the weights are read twice.
-            const int64_t h0 = T / 2;
             const int rc = run_qmv(parts, n, st, x, x_dtype, x_stride, y, y_dtype, y_stride, h0, e, act, nullptr);
             if (rc != MLXQ_OK) return rc;
             return run_qmv(parts, n, st, static_cast<const char*>(x) + static_cast<size_t>(h0) * x_stride * dtype_size(x_dtype), x_dtype, x_stride,
                            static_cast<char*>(y) + static_cast<size_t>(h0) * y_stride * dtype_size(y_dtype), y_dtype, y_stride, T - h0, e, act, nullptr);
         }
-        cudaError_t err = rsmem ? launch_qmv_pipe(parts[0]->bits, mp, pp, rsmem, parts[0]->device, st)
-                                : launch_qmv_mma(parts[0]->bits, mp, smem, parts[0]->device, st);
-        if (err != cudaSuccess) return cuda_fail(err, "qmv (tensor-core) launch");
-        return MLXQ_OK;
+        if (rsmem || smem) {
+            cudaError_t err = rsmem ? launch_qmv_pipe(parts[0]->bits, mp, pp, rsmem, parts[0]->device, st)
+                                    : launch_qmv_mma(parts[0]->bits, mp, smem, parts[0]->device, st);
+            if (err != cudaSuccess) return cuda_fail(err, "qmv (tensor-core) launch");
+            return MLXQ_OK;
+        }
     }
     if (peer) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
     // gridDim.y carries token tiles of four; walk very long batches in slices.

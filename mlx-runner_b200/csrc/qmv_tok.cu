@@ -115,16 +115,21 @@ size_t qmv_tok_plan(int bits, const MmaParams& p, int tokens, int sms, TokPlan& 
     for (int parities = 2; parities >= 1 && best_cost < 0; parities--)
     for (int ks = 1; ks <= warps; ks *= 2) {
         const int off_tab = align_up(off_fixed + parities * warps * 16 * tp.tp * 4, 128);
-        if (groups % ks != 0) break;
-        const int slice = groups / ks;
-        if (slice % 2 != 0 || slice < 2) break;
+        // slices are cut at even groups; the shortest must hold a pair, the longest sets the tables' size
+        int slice = 0, slice_min = groups;
+        for (int kw = 0; kw < ks; kw++) {
+            const int a = (((groups / 2) * kw) / ks) * 2, b = (((groups / 2) * (kw + 1)) / ks) * 2;
+            if (b - a > slice) slice = b - a;
+            if (b - a < slice_min) slice_min = b - a;
+        }
+        if (slice_min < 2) break;
         if (ks > 1 && warps / ks > 15) continue;                       // one named barrier per group of warps
         const int n_groups = warps / ks;
         const long long rounds = (cta_blocks + n_groups - 1) / n_groups;
         const long long cost = rounds * (slice + 2);                   // (ending a block and meeting the group: about two groups' work)
         const int nwin = (slice + 7) / 8;
         for (int depth = gb >= 16 ? 4 : 8; depth >= 2; depth /= 2) {
-            const int ntab = depth / slice + 2;
+            const int ntab = depth / slice_min + 2;
             const long long total = static_cast<long long>(off_tab) + static_cast<long long>(warps) * ntab * nwin * 512;
             const long long ring_at = (total + 127) / 128 * 128;
             const long long end = ring_at + static_cast<long long>(warps) * depth * slot_bytes;

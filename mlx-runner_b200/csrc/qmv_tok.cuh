@@ -28,7 +28,7 @@ struct TokPlan {
     int depth;           // ring slots (groups in flight) per warp: 8, 4 or 2
     int ntab;            // buffers of the per-block (scale, bias) cells: blocks the copy cursor may run ahead, plus two
     int nwin;            // windows of eight groups per warp slice
-    int slice_groups;    // groups per warp slice (even)
+    int slice_groups;    // groups of the longest warp slice (slices are cut at even groups: floor(pairs * kw / ks) * 2)
     int grid, n_blocks, base_blocks, extra_blocks;
     int cpr_shift;       // log2(in_dim / 8) when that is a power of two, else -1
     int xstride;         // halves between staged activation columns
@@ -106,7 +106,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const size_t row_bytes = static_cast<size_t>(K) * BITS / 8;
-    const int depth = tp.depth, ntab = tp.ntab, nwin = tp.nwin, slice_groups = tp.slice_groups, TP = tp.tp, gpad = tp.gpad;
+    const int depth = tp.depth, ntab = tp.ntab, nwin = tp.nwin, TP = tp.tp, gpad = tp.gpad;
 
     // Dependent launch, as in qmv_pipe.cuh: the layer's constants are fetched before griddepcontrol.wait, the
     // activations, the gate vector and y are touched after it.
@@ -115,7 +115,9 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
 
     // this warp's place: group `gi` of warps in the CTA, slice `kw` of K
     const int ks = tp.ks, gi = warp >> tp.ks_shift, kw = warp & (ks - 1), n_groups = TOK_WARPS >> tp.ks_shift;
-    const int gmin = kw * slice_groups;                        // first quantisation group of the slice
+    // the slice: quantisation groups [gmin, gmin + slice_groups), cut at even groups so that (scale, bias) pairs stay whole
+    const int gmin = (((groups >> 1) * kw) >> tp.ks_shift) << 1;
+    const int slice_groups = ((((groups >> 1) * (kw + 1)) >> tp.ks_shift) << 1) - gmin;
     // A group's bytes of the warp's sixteen rows lie row after row in a slot (RB bytes each); the warp copies them as
     // 16-byte pieces, lane l the pieces l, l + 32, ... below NPIECE, so that the copies read whole sectors whatever
     // the width; a lane then consumes GB bytes at GB * t of rows g and g + 8, which other lanes may have copied.
