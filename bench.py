@@ -80,14 +80,14 @@ def workload(args):
     """Description shared by both arms: config dict, algorithmic bytes of one step on the whole job."""
     if args.config == "c5":
         per_call = alg_bytes(C5_ROWS, C5_K, args.bits, 64, args.batch)
-        calls = args.calls or 48
+        calls = args.calls or 64
         return {"workload": f"vocabulary head {C5_ROWS}x{C5_K} b{args.bits} g64, batch {args.batch}, fp16 x, fp32 logits; "
                             f"{calls} calls per step ({per_call / 1e6:.0f} MB per call > L2)",
                 "rows": C5_ROWS, "in_dim": C5_K, "bits": args.bits, "group_size": 64, "batch": args.batch,
                 "launches_per_step": calls, "l2": "inputs larger than L2"}, per_call * calls
     if args.config == "c4":
         per_walk = C4_LAYERS * sum(alg_bytes(o, k, 4, 64, args.batch) for _, o, k in C4_PROJ)
-        walks = args.calls or 4
+        walks = args.calls or 6
         return {"workload": f"projection walk of a {C4_LAYERS}-layer transformer (hidden 4096, q|k|v 6144, gate|up 24576, down from 12288), "
                             f"b4 g64, batch {args.batch}, fp16 x, fp32 y; {walks} walks per step ({per_walk / 1e9:.2f} GB per walk > L2)",
                 "layers": C4_LAYERS, "bits": 4, "group_size": 64, "batch": args.batch,
@@ -378,7 +378,7 @@ def run_ours(args):
             else:
                 lin = mlxq.Linear(w, s, b, None, inDim=K, name=f"call{i}", device=local)
             distinct[i] = (lin, K, O)
-        n_rep = args.calls or (48 if args.config == "c5" else 4)
+        n_rep = args.calls or (64 if args.config == "c5" else 6)
         calls = [distinct[i] for _ in range(n_rep) for i in range(len(shapes))]
     ks = sorted({k for _, k, _ in calls})
     x_host = {k: torch.from_numpy(synth.make_activations(batch, k, synth.F16, seed=7 + k)[0].view(np.int16)).view(torch.float16).pin_memory() for k in ks}
