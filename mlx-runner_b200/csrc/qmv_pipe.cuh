@@ -2,13 +2,15 @@
 // asynchronous copies and laid out so that consecutive launches of a stream overlap.
 //
 // One CTA per SM walks the layer's 16-row blocks.  `ks` consecutive warps form a group that shares a block along
-// K; the groups of a CTA take alternate blocks.  A lane needs exactly the same bytes of every block -- 16 (4/8/2-bit)
-// or 24/40 (6/3/5-bit) bytes of rows g and g + 8 per step, plus the (scale, bias) pairs of its two accumulator
-// columns when a step ends a drain cycle -- so each lane fetches its own bytes with cp.async into its own cells of
-// a small ring in shared memory, several steps ahead, and reads them back with conflict-free 128-bit loads.
-// Nothing is shared between lanes on this path: no barrier, no mbarrier, no fence, just cp.async.wait_group.  The
-// ring is deep enough to run across block boundaries, and its first turn is issued before griddepcontrol.wait, i.e.
-// while the previous launch of the stream is still finishing (packed weights, scales and biases are the layer's
+// K; the groups of a CTA take alternate blocks.  A warp needs exactly the same bytes of every block -- per step, 64
+// (4/8/2-bit), 96 (6/3-bit) or 160 (5-bit) bytes of each of its sixteen rows, plus the (scale, bias) pairs of its
+// lanes' accumulator columns when a step ends a drain cycle -- so it fetches them with cp.async into a small ring of
+// its own in shared memory, several steps ahead: the rows as 16-byte pieces dealt out over the lanes (whole sectors
+// per copy instruction at every width), the pairs by the lanes that use them.  At 2, 4 and 8 bits a lane's pieces
+// are exactly the bytes it consumes and nothing is shared between lanes: no barrier, no mbarrier, no fence, just
+// cp.async.wait_group; at 3, 5 and 6 bits a __syncwarp on either side of the read orders the lanes.  The ring is
+// deep enough to run across block boundaries, and its first turn is issued before griddepcontrol.wait, i.e. while
+// the previous launch of the stream is still finishing (packed weights, scales and biases are the layer's
 // constants); the activations, the gate vector and y are only touched after it.  The activations are staged once
 // per CTA.  At the end of a block every warp of a group leaves a compact [16 rows x tokens] partial sum in shared
 // memory, the group meets on its named barrier, and its first warp adds the partials in warp order, applies row

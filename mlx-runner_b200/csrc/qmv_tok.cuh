@@ -3,9 +3,9 @@
 //
 // The one-token kernel (qmv_pipe.cuh) spends its spare accumulator columns on groups; with eight tokens there are no
 // spare columns, and a step of that kernel's size mixes two or four groups in the k dimension of one MMA.  Here a
-// step IS one group: lane (g, t) fetches GS / 4 codes of rows g and g + 8 (4 ... 32 bytes, the four lanes of a row
-// one contiguous run of GS codes), the group's MMAs accumulate into fresh registers, and the drain is four FMAs per
-// eight tokens: yacc += scale[row, group] * c.  The bias term sum_g bias[row, g] * xsum[g, token] is a small matrix
+// step IS one group: lane (g, t) consumes GS / 4 codes of rows g and g + 8 (4 ... 32 bytes, the four lanes of a row
+// one contiguous run of GS codes; the warp copies the sixteen rows' bytes piece-wise, see below), the group's MMAs
+// accumulate into fresh registers, and the drain is four FMAs per eight tokens: yacc += scale[row, group] * c.  The bias term sum_g bias[row, g] * xsum[g, token] is a small matrix
 // product of its own: eight groups at a time go through one mma.m16n8k8 in TF32 -- a 16-bit bias is exact in TF32,
 // and the fp32 group sums of the activations are split into three TF32 parts (11 + 11 + 2 mantissa bits), so the
 // products are exact and the sum is an fp32 sum like the FMA chain it replaces.
