@@ -25,7 +25,7 @@ bool supported(int bits, int gs) {
     return nm >= 2 && nm % 2 == 0;
 }
 
-template <int BITS, int GS, int NP>
+template <int BITS, int GS, int NP, int DEPTH_CT>
 cudaError_t launch_one(const MmaParams& p, const TokPlan& tp, size_t smem, int device, cudaStream_t st) {
     if constexpr (!TokUnit<BITS, GS>::SUPPORTED) {
         return cudaErrorNotSupported;
@@ -37,7 +37,7 @@ cudaError_t launch_one(const MmaParams& p, const TokPlan& tp, size_t smem, int d
         {
             std::lock_guard<std::mutex> lk(mu);
             if (!done[device]) {
-                const cudaError_t e = cudaFuncSetAttribute(qmv_tok_kernel<BITS, GS, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_WHOLE);
+                const cudaError_t e = cudaFuncSetAttribute(qmv_tok_kernel<BITS, GS, NP, DEPTH_CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_WHOLE);
                 if (e != cudaSuccess) return e;
                 done[device] = true;
             }
@@ -52,13 +52,20 @@ cudaError_t launch_one(const MmaParams& p, const TokPlan& tp, size_t smem, int d
         la[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = la;
         cfg.numAttrs = pdl_enabled() ? 1 : 0;
-        return cudaLaunchKernelEx(&cfg, qmv_tok_kernel<BITS, GS, NP>, p, tp);
+        return cudaLaunchKernelEx(&cfg, qmv_tok_kernel<BITS, GS, NP, DEPTH_CT>, p, tp);
     }
+}
+
+template <int BITS, int GS, int NP>
+cudaError_t launch_depth(const MmaParams& p, const TokPlan& tp, size_t smem, int device, cudaStream_t st) {
+    // the width's usual ring depth is compiled in; a shallower ring (shared memory short) takes the general instance
+    constexpr int usual = GS * BITS / 32 >= 16 ? 4 : 8;
+    return tp.depth == usual ? launch_one<BITS, GS, NP, usual>(p, tp, smem, device, st) : launch_one<BITS, GS, NP, 0>(p, tp, smem, device, st);
 }
 
 template <int BITS, int GS>
 cudaError_t launch_np(const MmaParams& p, const TokPlan& tp, size_t smem, int device, cudaStream_t st) {
-    return p.xn <= 8 ? launch_one<BITS, GS, 1>(p, tp, smem, device, st) : launch_one<BITS, GS, 2>(p, tp, smem, device, st);
+    return p.xn <= 8 ? launch_depth<BITS, GS, 1>(p, tp, smem, device, st) : launch_depth<BITS, GS, 2>(p, tp, smem, device, st);
 }
 
 template <int BITS>

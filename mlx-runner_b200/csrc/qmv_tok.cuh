@@ -51,7 +51,7 @@ template <int BITS, int GS> struct TokUnit {
     static constexpr int CL = GS / 4;                                           // codes per lane and group
     static constexpr int NM = CL / 4;                                           // MMAs per group
     static constexpr int RB = 4 * GB;                                           // bytes of a row per group
-    static constexpr int PIECE = RB % 16 == 0 ? 16 : 8;                         // bytes per asynchronous copy
+    static constexpr int PIECE = RB % 16 == 0 && GB != 8 ? 16 : 8;              // bytes per asynchronous copy (8-byte runs: every lane copies its own)
     static constexpr bool SUPPORTED = (GS * BITS) % 64 == 0 && GB >= 4 && NM >= 2 && NM % 2 == 0 && (WORDS || planned_width<BITS>());
     static constexpr uint32_t SLOT = 16 * RB;
 };
@@ -76,17 +76,8 @@ __device__ __forceinline__ void mma1688_tf32(float (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// the two 16-bit values of a word as fp32 bit patterns
-__device__ __forceinline__ void pair_to_f32(uint32_t u, int dt, uint32_t& lo, uint32_t& hi) {
-    if (dt == DT_F16) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
-        lo = __float_as_uint(f.x); hi = __float_as_uint(f.y);
-    } else {
-        lo = u << 16; hi = u & 0xFFFF0000u;
-    }
-}
-
-template <int BITS, int GS, int NP>
+// DEPTH_CT: the ring depth when it is the width's usual one (compiled in), 0 when the planner had to take a shallower ring.
+template <int BITS, int GS, int NP, int DEPTH_CT>
 __global__ void __launch_bounds__(TOK_WARPS * 32, 1)
 qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokPlan tp) {
     using U = TokUnit<BITS, GS>;
@@ -106,7 +97,7 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const size_t row_bytes = static_cast<size_t>(K) * BITS / 8;
-    const int depth = tp.depth, ntab = tp.ntab, nwin = tp.nwin, TP = tp.tp, gpad = tp.gpad;
+    const int depth = DEPTH_CT ? DEPTH_CT : tp.depth, ntab = tp.ntab, nwin = tp.nwin, TP = tp.tp, gpad = tp.gpad;
 
     // Dependent launch, as in qmv_pipe.cuh: the layer's constants are fetched before griddepcontrol.wait, the
     // activations, the gate vector and y are touched after it.
@@ -124,13 +115,14 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
     // (Rows of 24 or 40 bytes per group -- 3- and 5-bit at group 64, 6-bit at group 32 -- go as 8-byte pieces, and a
     // lane's 6- or 10-byte run then starts on a half word: it loads the words around it and shifts by 0 or 16 bits.)
     constexpr int RB = U::RB, PIECE = U::PIECE, PPR = RB / PIECE, NPIECE = 16 * PPR, NPT = (NPIECE + 31) / 32;
-    constexpr bool OWN_BYTES = GB == 16;                       // the lane's pieces are exactly the bytes it consumes
+    constexpr bool OWN_BYTES = GB == 16 || GB == 8;            // the lane's pieces are exactly the bytes it consumes
     const uint32_t ring = smem_u32(smem_tok + tp.off_ring) + warp * (depth * SLOT) + lane * PIECE;
     const uint32_t ring_end = ring + depth * SLOT;
     const uint32_t rd_delta = static_cast<uint32_t>(g * RB + ((t * GB) & ~3) - lane * PIECE);
     const uint32_t rd_shift = static_cast<uint32_t>(((t * GB) & 3) * 8);     // 0 or 16 (0 when the run starts on a word)
     const uint32_t tab = smem_u32(smem_tok + tp.off_tab) + warp * (ntab * nwin * 512) + lane * 16;
     const uint32_t zaddr0 = smem_u32(smem_tok + tp.off_zero);
+    const bool s_f16 = q.s_dtype == DT_F16;
     // The lane's (scale, bias) cells start as zeros and the copies only ever fill the pairs inside the slice, so a
     // window's tail past the slice multiplies by zero.
     for (int c = 0; c < ntab * nwin; c++) asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(tab + c * 512), "r"(0u) : "memory");
@@ -343,7 +335,8 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
 #pragma unroll 1
         for (int gl = 0; gl < slice_groups; gl++) {
             const int gw = gl & 7;                              // the group's place in its window of eight
-            if (depth == 8) asm volatile("cp.async.wait_group 7;" ::: "memory");
+            if constexpr (DEPTH_CT != 0) asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH_CT - 1) : "memory");
+            else if (depth == 8) asm volatile("cp.async.wait_group 7;" ::: "memory");
             else if (depth == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
             else asm volatile("cp.async.wait_group 1;" ::: "memory");
             if constexpr (!OWN_BYTES) __syncwarp();             // (the bytes a lane consumes were copied by other lanes)
@@ -352,14 +345,18 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
                 uint32_t s0, s1, b0, b1;
                 asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(s0), "=r"(s1), "=r"(b0), "=r"(b1) : "r"(cell));
                 cell += 512;
-                uint32_t u0, u1, u2, u3;
-                pair_to_f32(s0, q.s_dtype, u0, u1);
-                pair_to_f32(s1, q.s_dtype, u2, u3);
-                sf0 = __uint_as_float(u0); sf1 = __uint_as_float(u1); sf2 = __uint_as_float(u2); sf3 = __uint_as_float(u3);
                 // bias term of the window's eight groups: k slot t is group 2t, slot t + 4 is group 2t + 1
                 uint32_t a0, a1, a2, a3;
-                pair_to_f32(b0, q.s_dtype, a0, a2);
-                pair_to_f32(b1, q.s_dtype, a1, a3);
+                if (s_f16) {
+                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&s0)), f1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
+                    const float2 g0 = __half22float2(*reinterpret_cast<const __half2*>(&b0)), g1 = __half22float2(*reinterpret_cast<const __half2*>(&b1));
+                    sf0 = f0.x; sf1 = f0.y; sf2 = f1.x; sf3 = f1.y;
+                    a0 = __float_as_uint(g0.x); a2 = __float_as_uint(g0.y); a1 = __float_as_uint(g1.x); a3 = __float_as_uint(g1.y);
+                } else {
+                    sf0 = __uint_as_float(s0 << 16); sf1 = __uint_as_float(s0 & 0xFFFF0000u);
+                    sf2 = __uint_as_float(s1 << 16); sf3 = __uint_as_float(s1 & 0xFFFF0000u);
+                    a0 = b0 << 16; a2 = b0 & 0xFFFF0000u; a1 = b1 << 16; a3 = b1 & 0xFFFF0000u;
+                }
 #pragma unroll
                 for (int ps = 0; ps < NP; ps++) {
 #pragma unroll
