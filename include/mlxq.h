@@ -163,6 +163,20 @@ MLXQ_API int mlxq_linear_lookup(mlxq_linear_t h, mlxq_stream_t stream, const int
 MLXQ_API int mlxq_linear_forward_rows(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, float* y,
                                       const uint32_t* count, const int32_t* list, int64_t max_rows);
 
+/* First pass of the token selection (sample_blocks, Kernels.swift:2339-2377): for every token t and every block b of
+ * 256 logits, the block's maximum and the lowest index that holds it.  logits is fp32 [T, stride] on `device`;
+ * pairs receives the maxima as fp32 [T][nb] followed by the indices as int32 [T][nb], nb = ceil(V / 256)
+ * (2 * T * nb 4-byte words).  index_base is added to every index (a shard's first row).  A NaN never wins; a block
+ * with no value above -inf reports the index 0x7fffffff. */
+MLXQ_API int mlxq_block_max(mlxq_stream_t stream, int device, const float* logits, int64_t stride, int64_t V, int64_t T,
+                            int32_t index_base, uint32_t* pairs);
+
+/* Greedy second pass (the argmax branch of sample_token, Kernels.swift:2379 ff.): token[t] = the lowest index holding
+ * the maximum over n_seg segments of block maxima, each laid out as mlxq_block_max writes them (segment s starts
+ * 2 * T * nb words after segment s - 1); value[t] (optional) = that maximum.  0x7fffffff when no block has one. */
+MLXQ_API int mlxq_block_argmax(mlxq_stream_t stream, int device, const uint32_t* pairs, int n_seg, int64_t T, int64_t nb,
+                               int32_t* token, float* value);
+
 /* Writes the codes of every weight as one byte each, u8 [out_dim, in_dim].  The GPU half of the
  * bit-exact unpack check (unpack8, Kernels.swift:34-55). */
 MLXQ_API int mlxq_unpack_codes(mlxq_linear_t h, mlxq_stream_t stream, uint8_t* out);
@@ -235,6 +249,15 @@ MLXQ_API int mlxq_comm_window(mlxq_comm_t c, size_t bytes);
 MLXQ_API int mlxq_linear_forward_gather_fused(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t stream, const void* x,
                                               int x_dtype, int64_t x_stride, int64_t T, float** y_full);
 MLXQ_API int mlxq_comm_wait(mlxq_comm_t c, mlxq_stream_t stream);
+
+/* Vocabulary head sharded by rows with the selection's first pass folded in (Transformer.swift:1574, 1588-1611 on
+ * one GPU; no counterpart for the sharding): the shard's logits go to y_local (fp32 [T, shard rows], the caller's
+ * scratch), their block maxima -- indices counted in the full vocabulary -- to this rank's segment of `pairs`
+ * (n ranks x 2 * T * nb words, nb = ceil(shard rows / 256)), and only those segments are gathered (ncclAllGather):
+ * 8 bytes per 256 logits cross NVLink instead of 1024.  Every rank's shard must have the same number of rows.
+ * mlxq_block_argmax(pairs, n ranks, T, nb) then gives the greedy token on every rank. */
+MLXQ_API int mlxq_linear_forward_blockmax_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t stream, const void* x,
+                                                 int x_dtype, int64_t x_stride, int64_t T, float* y_local, uint32_t* pairs);
 
 #ifdef __cplusplus
 }

@@ -62,6 +62,8 @@ SIGNATURES = {
     "mlxq_linear_forward_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                            C.c_void_p, C.c_int64]),
     "mlxq_unpack_codes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mlxq_block_max": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
+    "mlxq_block_argmax": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "mlxq_fusable": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
     "mlxq_can_fuse": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int64]),
     "mlxq_use_gemm64": (C.c_int, [C.c_int64, C.c_int64]),
@@ -77,6 +79,8 @@ SIGNATURES = {
                                              C.c_void_p, C.c_int64, C.c_int64]),
     "mlxq_comm_window": (C.c_int, [C.c_void_p, C.c_size_t]),
     "mlxq_comm_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mlxq_linear_forward_blockmax_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
+                                                      C.c_int64, C.c_void_p, C.c_void_p]),
     "mlxq_linear_forward_gather_fused": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
                                                    C.c_int64, C.POINTER(C.c_void_p)]),
 }

@@ -605,6 +605,27 @@ int mlxq_linear_forward_rows(mlxq_linear_t h, mlxq_stream_t stream, const void* 
     return err == cudaSuccess ? MLXQ_OK : cuda_fail(err, "row-list launch");
 }
 
+int mlxq_block_max(mlxq_stream_t stream, int device, const float* logits, int64_t stride, int64_t V, int64_t T,
+                   int32_t index_base, uint32_t* pairs) {
+    if (!logits || !pairs) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (V < 1 || T < 0 || stride < V || V > 0x7fffff00ll || index_base < 0 || static_cast<int64_t>(index_base) + V > 0x7fffff00ll)
+        return fail(MLXQ_INVALID_ARGUMENT, "V %lld, T %lld, stride %lld, index base %d", (long long)V, (long long)T, (long long)stride, index_base);
+    DeviceGuard guard(device);
+    if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", device);
+    cudaError_t err = launch_block_max(logits, stride, V, T, index_base, pairs, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? MLXQ_OK : cuda_fail(err, "block maxima launch");
+}
+
+int mlxq_block_argmax(mlxq_stream_t stream, int device, const uint32_t* pairs, int n_seg, int64_t T, int64_t nb,
+                      int32_t* token, float* value) {
+    if (!pairs || !token) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (n_seg < 1 || T < 0 || nb < 1 || nb * n_seg > 0x7fffffffll) return fail(MLXQ_INVALID_ARGUMENT, "%d segments of %lld blocks, T %lld", n_seg, (long long)nb, (long long)T);
+    DeviceGuard guard(device);
+    if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", device);
+    cudaError_t err = launch_block_argmax(pairs, n_seg, T, static_cast<int>(nb), token, value, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? MLXQ_OK : cuda_fail(err, "block argmax launch");
+}
+
 int mlxq_unpack_codes(mlxq_linear_t h, mlxq_stream_t stream, uint8_t* out) {
     if (!h || !out) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
     if (reinterpret_cast<uintptr_t>(out) % 8 != 0) return fail(MLXQ_INVALID_ARGUMENT, "out must be 8-byte aligned");

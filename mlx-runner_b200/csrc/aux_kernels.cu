@@ -110,4 +110,97 @@ cudaError_t launch_rows(const uint8_t* w, const void* scales, const void* biases
     return cudaGetLastError();
 }
 
+// ---- token selection, first pass (sample_blocks, Kernels.swift:2339-2377) -------------------------------------------
+// One warp per block of 256 logits: lane l scans eight contiguous values in index order with a strict `>` (so a NaN
+// never wins and the lowest index of equal values does), then the warp takes the maximum and, among the lanes that
+// hold it, the lowest index.  bmax[t][b] / barg[t][b]; a block without any value above -inf reports SELECT_NONE.
+__global__ void block_max_kernel(const float* __restrict__ logits, long long stride, long long V, int nb, long long T,
+                                 int index_base, float* __restrict__ bmax, int* __restrict__ barg, int vec_ok) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= T * nb) return;
+    const long long t = wid / nb;
+    const int b = static_cast<int>(wid - t * nb);
+    const float* row = logits + t * stride;
+    const long long i0 = static_cast<long long>(b) * SELECT_BLOCK + lane * 8;
+    float best = -INFINITY;
+    int bi = SELECT_NONE;
+    if (vec_ok && i0 + 8 <= V) {
+        const float4 a = *reinterpret_cast<const float4*>(row + i0), c = *reinterpret_cast<const float4*>(row + i0 + 4);
+        const float v[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int j = 0; j < 8; j++) if (v[j] > best) { best = v[j]; bi = static_cast<int>(i0) + j; }
+    } else {
+        for (long long i = i0; i < V && i < i0 + 8; i++) { const float v = row[i]; if (v > best) { best = v; bi = static_cast<int>(i); } }
+    }
+    float m = best;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    int idx = best == m ? bi : SELECT_NONE;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) idx = min(idx, __shfl_xor_sync(0xffffffffu, idx, o));
+    if (lane == 0) {
+        bmax[t * nb + b] = m;
+        barg[t * nb + b] = idx == SELECT_NONE ? SELECT_NONE : idx + index_base;
+    }
+}
+
+// ---- token selection, greedy second pass: the maximum over the blocks of every segment and the lowest index that
+// holds it (the argmax branch of sample_token, Kernels.swift:2379 ff.) -- one CTA per token --------------------------
+__global__ void block_argmax_kernel(const uint32_t* __restrict__ pairs, int n_seg, long long T, int nb, int* __restrict__ token,
+                                    float* __restrict__ value) {
+    __shared__ float sm[8];
+    __shared__ int si[8];
+    const long long t = blockIdx.x;
+    const long long seg_words = 2 * T * nb;
+    float best = -INFINITY;
+    int bi = SELECT_NONE;
+    for (int i = threadIdx.x; i < n_seg * nb; i += blockDim.x) {
+        const int seg = i / nb, b = i - seg * nb;
+        const uint32_t* base = pairs + seg * seg_words;
+        const float m = __uint_as_float(base[t * nb + b]);
+        const int ix = static_cast<int>(base[T * nb + t * nb + b]);
+        if (m > best || (m == best && ix < bi)) { best = m; bi = ix; }
+    }
+    float m = best;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    int idx = best == m ? bi : SELECT_NONE;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) idx = min(idx, __shfl_xor_sync(0xffffffffu, idx, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sm[warp] = m; si[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        float mm = lane < nw ? sm[lane] : -INFINITY;
+        const int ii = lane < nw ? si[lane] : SELECT_NONE;
+        float top = mm;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+        int idx2 = mm == top ? ii : SELECT_NONE;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) idx2 = min(idx2, __shfl_xor_sync(0xffffffffu, idx2, o));
+        if (lane == 0) { token[t] = idx2; if (value) value[t] = top; }
+    }
+}
+
+cudaError_t launch_block_max(const float* logits, long long stride, long long V, long long T, int index_base, uint32_t* pairs,
+                             cudaStream_t st) {
+    if (T == 0 || V == 0) return cudaSuccess;
+    const int nb = static_cast<int>((V + SELECT_BLOCK - 1) / SELECT_BLOCK);
+    const int warps = 8;
+    const long long n = T * nb;
+    const int vec_ok = (reinterpret_cast<uintptr_t>(logits) % 16 == 0 && stride % 4 == 0) ? 1 : 0;
+    block_max_kernel<<<static_cast<unsigned>((n + warps - 1) / warps), warps * 32, 0, st>>>(
+        logits, stride, V, nb, T, index_base, reinterpret_cast<float*>(pairs), reinterpret_cast<int*>(pairs) + T * nb, vec_ok);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_block_argmax(const uint32_t* pairs, int n_seg, long long T, int nb, int32_t* token, float* value, cudaStream_t st) {
+    if (T == 0) return cudaSuccess;
+    block_argmax_kernel<<<static_cast<unsigned>(T), 256, 0, st>>>(pairs, n_seg, T, nb, token, value);
+    return cudaGetLastError();
+}
+
 }  // namespace mlxq

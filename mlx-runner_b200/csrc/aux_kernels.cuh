@@ -12,4 +12,12 @@ cudaError_t launch_rows(const uint8_t* w, const void* scales, const void* biases
                         float* y, const uint32_t* count, const int32_t* list, long long max_rows, int rows, int K, int gs,
                         int bits, cudaStream_t st);
 
+// First pass of the token selection (block maxima) and the greedy second pass over them.  `pairs` holds, per segment,
+// the maxima as fp32 [T][nb] followed by their indices as int32 [T][nb].
+constexpr int SELECT_BLOCK = 256;            // logits per block
+constexpr int SELECT_NONE = 0x7fffffff;      // index of a block (or a token) with no value above -inf
+cudaError_t launch_block_max(const float* logits, long long stride, long long V, long long T, int index_base, uint32_t* pairs,
+                             cudaStream_t st);
+cudaError_t launch_block_argmax(const uint32_t* pairs, int n_seg, long long T, int nb, int32_t* token, float* value, cudaStream_t st);
+
 }  // namespace mlxq

@@ -10,6 +10,7 @@
 
 #include "../../include/mlxq.h"
 #include "api_internal.h"
+#include "aux_kernels.cuh"
 
 namespace {
 
@@ -191,6 +192,29 @@ int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t str
     }
     r = n.GroupEnd();
     if (r != ncclSuccess) return nccl_fail(r, "ncclGroupEnd");
+    return MLXQ_OK;
+}
+
+int mlxq_linear_forward_blockmax_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_stream_t stream, const void* x, int x_dtype,
+                                        int64_t x_stride, int64_t T, float* y_local, uint32_t* pairs) {
+    if (!h || !c || !y_local || !pairs) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (h->shard_count != c->size || h->shard_rank != c->rank)
+        return mlxq::fail(MLXQ_INVALID_ARGUMENT, "layer is shard %d of %d but the communicator is rank %d of %d",
+                          h->shard_rank, h->shard_count, c->rank, c->size);
+    if (h->out_dim * c->size != h->total_out)
+        return mlxq::fail(MLXQ_UNSUPPORTED, "shards of unequal size (%lld rows of %lld on %d ranks)", (long long)h->out_dim, (long long)h->total_out, c->size);
+    if (T < 1 || h->total_out > 0x7fffff00ll) return mlxq::fail(MLXQ_INVALID_ARGUMENT, "T %lld, %lld rows", (long long)T, (long long)h->total_out);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = mlxq::forward_impl(h, st, x, x_dtype, x_stride, y_local, MLXQ_F32, h->out_dim, T);
+    if (rc != MLXQ_OK) return rc;
+    const int64_t nb = (h->out_dim + mlxq::SELECT_BLOCK - 1) / mlxq::SELECT_BLOCK;
+    const size_t seg = static_cast<size_t>(2) * T * nb;
+    uint32_t* mine = pairs + seg * c->rank;
+    cudaError_t e = mlxq::launch_block_max(y_local, h->out_dim, h->out_dim, T, static_cast<int>(h->row_offset), mine, st);
+    if (e != cudaSuccess) return mlxq::cuda_fail(e, "block maxima launch");
+    if (c->size == 1) return MLXQ_OK;
+    ncclResult_t r = nccl().AllGather(mine, pairs, seg, ncclFloat32, c->comm, st);      // (raw 4-byte words)
+    if (r != ncclSuccess) return nccl_fail(r, "ncclAllGather (block maxima)");
     return MLXQ_OK;
 }
 

@@ -358,6 +358,23 @@ class Linear:
         return staging
 
 
+SELECT_BLOCK = 256          # logits per block of the selection's first pass
+SELECT_NONE = 0x7FFFFFFF    # index reported for a block (or token) with no value above -inf
+
+
+def blockMax(stream, logits, V: int, T: int, stride: int, pairs, indexBase: int = 0, device: int = 0) -> None:
+    """First pass of the token selection (``sample_blocks``, ``Kernels.swift:2339-2377``): per token and block of 256
+    logits the maximum and the lowest index holding it.  ``pairs`` (int32 or uint32, 2 * T * nb words, nb =
+    ceil(V / 256)) receives the maxima as fp32 bit patterns [T][nb], then the indices [T][nb]."""
+    check(L.load().mlxq_block_max(_stream_handle(stream), device, _ptr(logits), stride, V, T, indexBase, _ptr(pairs)))
+
+
+def blockArgmax(stream, pairs, nSeg: int, T: int, nb: int, token, value=None, device: int = 0) -> None:
+    """Greedy second pass over ``nSeg`` segments of block maxima: token[t] = lowest index holding the maximum."""
+    check(L.load().mlxq_block_argmax(_stream_handle(stream), device, _ptr(pairs), nSeg, T, nb, _ptr(token),
+                                     _ptr(value) if value is not None else None))
+
+
 def streamStatus(stream=None, device: int = 0) -> None:
     """Wait for ``stream`` and raise if a kernel failed or recorded an error (``cb.error`` in the reference)."""
     check(L.load().mlxq_stream_status(_stream_handle(stream), device))
@@ -422,6 +439,15 @@ class Comm:
             view = torch.as_tensor(_DeviceArray(out.value, (T, layer.totalOut), self.device), device=f"cuda:{self.device}")
             self._views[key] = view
         return view
+
+    def forwardBlockMaxGather(self, layer: Linear, stream, x, xStride: int, T: int, yLocal, pairs,
+                              xDtype: Optional[int] = None) -> None:
+        """Row-sharded vocabulary head with the selection's first pass folded in: the shard's logits go to ``yLocal``
+        (fp32 [T, shard rows]), their block maxima (indices in the full vocabulary) to this rank's segment of ``pairs``
+        (nranks x 2 * T * nb words), and only the segments are gathered.  ``blockArgmax(pairs, nranks, T, nb)`` then
+        yields the greedy token."""
+        check(L.load().mlxq_linear_forward_blockmax_gather(layer._h, self._h, _stream_handle(stream), _ptr(x),
+                                                           _act_dtype(x, xDtype), xStride, T, _ptr(yLocal), _ptr(pairs)))
 
     def wait(self, stream) -> None:
         """Enqueue the wait for every peer's rows of the last fused call."""

@@ -310,3 +310,43 @@ class QuantFixture:
     def reference(self, x: np.ndarray) -> np.ndarray:
         """y [T, O]: double accumulate, cast, then add the row bias (KernelTests.swift:102-113)."""
         return matmul_dense(self.dense, x, self.bias)
+
+
+# ---- token selection, first pass and greedy second pass -----------------------------------------------------------
+SELECT_BLOCK = 256
+SELECT_NONE = 0x7FFFFFFF
+
+
+def block_max(logits: np.ndarray, index_base: int = 0):
+    """``sample_blocks`` / ``smp_block`` (Sources/MLXEngine/Kernels.swift:2339-2377): for every row of ``logits``
+    [T, V] and every block of 256 values, the maximum and the lowest index holding it.  The scan is a strict ``>``
+    from -inf in index order, so a NaN never wins and a block with nothing above -inf reports SELECT_NONE."""
+    logits = np.asarray(logits, dtype=np.float32)
+    T, V = logits.shape
+    nb = (V + SELECT_BLOCK - 1) // SELECT_BLOCK
+    bmax = np.full((T, nb), -np.inf, dtype=np.float32)
+    barg = np.full((T, nb), SELECT_NONE, dtype=np.int64)
+    for t in range(T):
+        for b in range(nb):
+            seg = logits[t, b * SELECT_BLOCK:(b + 1) * SELECT_BLOCK]
+            best, bi = np.float32(-np.inf), SELECT_NONE
+            for j, v in enumerate(seg):
+                if v > best:
+                    best, bi = v, b * SELECT_BLOCK + j + index_base
+            bmax[t, b], barg[t, b] = best, bi
+    return bmax, barg.astype(np.int32)
+
+
+def block_argmax(bmax: np.ndarray, barg: np.ndarray):
+    """The greedy branch of ``sample_token`` (Kernels.swift:2379 ff.) over block maxima [T, n]: the maximum and the
+    lowest index that holds it (SELECT_NONE when no block has a value above -inf)."""
+    T = bmax.shape[0]
+    tok = np.full(T, SELECT_NONE, dtype=np.int32)
+    val = np.full(T, -np.inf, dtype=np.float32)
+    for t in range(T):
+        best, bi = np.float32(-np.inf), SELECT_NONE
+        for m, ix in zip(bmax[t], barg[t]):
+            if m > best or (m == best and ix < bi):
+                best, bi = m, int(ix)
+        tok[t], val[t] = bi, best
+    return tok, val

@@ -58,6 +58,19 @@ def _worker(rank, world, port, q):
             got_nccl, got_fused = y.cpu().numpy(), out.cpu().numpy().copy()
             assert oracle.max_rel_err(got_nccl, ref) < 1e-3, f"rank {rank} call {it}: NCCL gather"
             assert oracle.max_rel_err(got_fused, ref) < 1e-3, f"rank {rank} call {it}: fused gather"
+            # the sharded head with the selection's first pass folded in: only block maxima are gathered, and the greedy
+            # token over them is the argmax of the gathered logits (same kernel, same rows: bit-identical values)
+            rows = O // world
+            nb = (rows + mlxq.SELECT_BLOCK - 1) // mlxq.SELECT_BLOCK
+            y_local = torch.zeros((T, rows), dtype=torch.float32, device=dev)
+            pairs = torch.zeros((world, 2, T, nb), dtype=torch.int32, device=dev)
+            token = torch.zeros(T, dtype=torch.int32, device=dev)
+            value = torch.zeros(T, dtype=torch.float32, device=dev)
+            comm.forwardBlockMaxGather(lin, None, x_dev, K, T, y_local, pairs)
+            mlxq.blockArgmax(None, pairs, world, T, nb, token, value, device=rank)
+            torch.cuda.synchronize()
+            assert np.array_equal(token.cpu().numpy(), got_nccl.argmax(axis=1).astype(np.int32)), f"rank {rank} call {it}: greedy token"
+            assert np.array_equal(value.cpu().numpy(), got_nccl.max(axis=1)), f"rank {rank} call {it}: greedy value"
             assert np.array_equal(got_nccl.view(np.uint32), got_fused.view(np.uint32)), "the two gathers disagree"
             dist.barrier()
         # a batch the decode kernel does not take is refused and leaves the communicator usable

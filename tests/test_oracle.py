@@ -196,3 +196,28 @@ def test_two_independent_restatements_agree(oracle):
         y = mr.qmm(lay.packed, lay.scales_raw, lay.biases_raw, sdt, x, 4096, bits, gs)
         ref = oracle.qmatmul(lay.packed, lay.scales_raw, lay.biases_raw, sdt, x, 4096, bits, gs)
         assert oracle.max_rel_err(y, ref) < 2e-5, (bits, gs)
+
+
+def test_block_maxima_and_greedy_token(oracle):
+    # sample_blocks / the argmax branch of sample_token (Kernels.swift:2339-2377): against plain numpy on rows with a
+    # ragged last block, equal maxima (the lowest index wins), NaNs (never win) and an all -inf block (reports none)
+    g = np.random.default_rng(5)
+    x = g.standard_normal((3, 256 * 3 + 77)).astype(np.float32)
+    x[0, 10] = x[0, 700] = 50.0                     # equal maxima in two blocks
+    x[1, 5] = np.nan
+    x[1, 256:512] = -np.inf
+    x[2, 800] = 7.5
+    bmax, barg = oracle.block_max(x, index_base=1000)
+    nb = bmax.shape[1]
+    assert nb == 4
+    for t in range(3):
+        for b in range(nb):
+            seg = x[t, b * 256:(b + 1) * 256]
+            if np.all(np.isneginf(seg) | np.isnan(seg)):
+                assert barg[t, b] == oracle.SELECT_NONE and np.isneginf(bmax[t, b])
+            else:
+                assert bmax[t, b] == np.nanmax(seg)
+                assert barg[t, b] == 1000 + b * 256 + int(np.nanargmax(seg))
+    tok, val = oracle.block_argmax(bmax, barg)
+    assert tok.tolist() == [1000 + 10, 1000 + int(np.nanargmax(x[1])), 1000 + 800]
+    assert val.tolist() == [50.0, float(np.nanmax(x[1])), 7.5]

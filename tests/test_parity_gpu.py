@@ -329,3 +329,28 @@ def test_tall_layers_and_larger_batches_run_clean(mlxq, oracle, bits, T, O):
     rows = np.sort(np.random.default_rng(O).choice(O, size=96, replace=False))
     ref = oracle.qmatmul(lay.packed[rows], lay.scales_raw[rows], lay.biases_raw[rows], synth.F16, x, K, bits, 64)
     assert oracle.max_rel_err(got[:, rows], ref) < 1e-3
+
+
+def test_block_maxima_and_greedy_token_are_exact(mlxq, oracle):
+    # first pass of the token selection and the greedy pass over it, bit for bit against the oracle: vocabulary-sized
+    # rows, a ragged last block, a row stride that breaks 16-byte alignment (scalar path), equal maxima, NaN, -inf
+    g = np.random.default_rng(9)
+    for V, T, stride in ((151936, 3, 151936), (1000, 4, 1003), (256, 1, 256), (37, 2, 40)):
+        x = g.standard_normal((T, stride)).astype(np.float32)
+        x[0, V // 3] = x[0, V // 3 + (300 if V > 600 else 1)] = 40.0
+        if T > 1:
+            x[1, : min(V, 256)] = np.where(np.arange(min(V, 256)) == 1, np.nan, -np.inf)
+        ref_m, ref_i = oracle.block_max(x[:, :V], index_base=77)
+        nb = ref_m.shape[1]
+        xd = torch.from_numpy(x).cuda()
+        pairs = torch.zeros((2, T, nb), dtype=torch.int32, device="cuda")
+        mlxq.blockMax(None, xd, V, T, stride, pairs, indexBase=77)
+        token = torch.zeros(T, dtype=torch.int32, device="cuda")
+        value = torch.zeros(T, dtype=torch.float32, device="cuda")
+        mlxq.blockArgmax(None, pairs, 1, T, nb, token, value)
+        torch.cuda.synchronize()
+        got = pairs.cpu().numpy()
+        assert np.array_equal(got[0].view(np.float32), ref_m), f"V {V}: block maxima"
+        assert np.array_equal(got[1], ref_i), f"V {V}: block indices"
+        tok, val = oracle.block_argmax(ref_m, ref_i)
+        assert np.array_equal(token.cpu().numpy(), tok) and np.array_equal(value.cpu().numpy(), val), f"V {V}: greedy token"
