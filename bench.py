@@ -551,6 +551,13 @@ def run_ours(args):
     # (at N > 1 that time includes the gather, so the N = 1 line is the kernel's figure).
     per_rank_bytes = step_bytes / (1 if args.config == "default" else world)
     achieved = per_rank_bytes * args.steps / (ms * 1e-3) / 1e9
+    select = None
+    if args.config == "c5":
+        try:
+            select = select_probe(mlxq, torch, dist if world > 1 else None, comm, last[0], x_dev[last[1]], last[1], batch, last[2], world, rank,
+                                  local, fused, y_dev, keep[-1], x_host[last[1]].float().numpy())
+        except Exception as e:      # noqa: BLE001
+            select = {"error": f"{type(e).__name__}: {str(e)[:120]}"}
     if rank == 0:
         probe = prefill_probe(mlxq, torch, device, peaks) if world == 1 and not args.no_prefill and args.config == "default" else {"available": False}
         cpu = cpu_sample(args, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
@@ -581,6 +588,8 @@ def run_ours(args):
                             "note": "the step without its gathers (shard matvecs only), then the difference"}
         if cpu:
             out["cpu_baseline"] = cpu
+        if select is not None:
+            out["select"] = select
         print(json.dumps(out), flush=True)
         if check.startswith("FAILED"):
             raise SystemExit(f"bench.py: {check}")
@@ -589,6 +598,92 @@ def run_ours(args):
         dist.barrier()
         comm.close()
         dist.destroy_process_group()
+
+
+def select_probe(mlxq, torch, dist, comm, lin, x, K, batch, total, world, rank, local, fused, y_dev, keep, x_np):
+    """Config 5 with greedy selection after the head: the full logits gathered and then scanned (block maxima over
+    the whole vocabulary, then the greedy pass), against the head whose shard kernel is followed by the block maxima
+    of the shard alone, so that only maxima are gathered.  Device time per token step from CUDA events around 32
+    steps enqueued back to back (one API call per launch: at 8 ranks the host's pace shows).  The tokens of the two
+    paths must agree on every rank, and the winner's logit is checked against the oracle."""
+    device = torch.device("cuda", local)
+    st = torch.cuda.current_stream()
+    rows = total // world
+    nb_full = (total + mlxq.SELECT_BLOCK - 1) // mlxq.SELECT_BLOCK
+    nb = (rows + mlxq.SELECT_BLOCK - 1) // mlxq.SELECT_BLOCK
+    y_local = torch.zeros((batch, rows), dtype=torch.float32, device=device)
+    pairs_full = torch.zeros((2, batch, nb_full), dtype=torch.int32, device=device)
+    pairs = torch.zeros((world, 2, batch, nb), dtype=torch.int32, device=device)
+    tok_a = torch.zeros(batch, dtype=torch.int32, device=device)
+    tok_b = torch.zeros(batch, dtype=torch.int32, device=device)
+    val_b = torch.zeros(batch, dtype=torch.float32, device=device)
+
+    def path_logits():
+        if comm is not None:
+            if fused:
+                out = comm.forwardGatherFused(lin, st, x, K, batch, wait=True)
+            else:
+                comm.forwardGather(lin, st, x, K, y_dev, total, batch)
+                out = y_dev[:, :total]
+        else:
+            lin.encode(st, x, K, y_dev, total, batch)
+            out = y_dev[:, :total]
+        mlxq.blockMax(st, out, total, batch, out.stride(0), pairs_full, device=local)
+        mlxq.blockArgmax(st, pairs_full, 1, batch, nb_full, tok_a, None, device=local)
+
+    def path_block_max():
+        if comm is not None:
+            comm.forwardBlockMaxGather(lin, st, x, K, batch, y_local, pairs)
+        else:
+            lin.encode(st, x, K, y_local, rows, batch)
+            mlxq.blockMax(st, y_local, rows, batch, rows, pairs, device=local)
+        mlxq.blockArgmax(st, pairs, world, batch, nb, tok_b, val_b, device=local)
+
+    def timed_us(fn, n=32):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms * 1e3 / n
+
+    us_a = timed_us(path_logits)
+    us_b = timed_us(path_block_max)
+    mlxq.streamStatus(st, local)
+    agree = bool(torch.equal(tok_a, tok_b))
+    winner_ok = True
+    try:
+        from oracle import oracle
+        w, s, b = keep
+        toks = tok_b.cpu().numpy()
+        mine = [(t, int(r) - lin.rowOffset) for t, r in enumerate(toks) if lin.rowOffset <= int(r) < lin.rowOffset + rows]
+        if mine:
+            ref = oracle_rows(torch, w, s, b, np.array(sorted({r for _, r in mine})), x_np, K, lin.bits, 64)
+            order = {r: i for i, r in enumerate(sorted({r for _, r in mine}))}
+            got = val_b.cpu().numpy()
+            winner_ok = all(abs(got[t] - ref[t, order[r]]) <= 1e-3 * max(1.0, abs(ref[t, order[r]])) for t, r in mine)
+    except Exception:       # noqa: BLE001
+        winner_ok = False
+    if world > 1:
+        flag = torch.tensor([1 if (agree and winner_ok) else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        agree = winner_ok = bool(flag.item())
+    return {"greedy_tokens_agree": agree, "winner_matches_oracle": winner_ok,
+            "logits_then_select_us_per_step": us_a, "block_max_gather_us_per_step": us_b,
+            "gathered_bytes_per_step": {"logits": int(total * 4 * batch) if world > 1 else 0,
+                                        "block_maxima": int(world * 2 * nb * 4 * batch) if world > 1 else 0},
+            "note": "head call + selection per token step; one API call per launch, CUDA events around 32 steps"}
 
 
 def run_sweep(args):
