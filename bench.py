@@ -578,7 +578,7 @@ def run_ours(args):
                          "traffic_source": NCU_TRAFFIC_SOURCE if captured_shape else None, "peak_source": peaks["source"],
                          "frac_of_nominal_8000": achieved / 8000.0, "bytes_per_step_per_gpu": per_rank_bytes},
             "api_calls": {"ms_per_step": ms_api, "value": scale * step_bytes / (ms_api * 1e-3) / 1e9,
-                          "note": "the same step with one API call per launch (the mode of sharded runs)"},
+                          "note": "the same step with one API call per launch"},
             "output_check": check,
             "prefill": probe,
         }
