@@ -354,3 +354,48 @@ def test_block_maxima_and_greedy_token_are_exact(mlxq, oracle):
         assert np.array_equal(got[1], ref_i), f"V {V}: block indices"
         tok, val = oracle.block_argmax(ref_m, ref_i)
         assert np.array_equal(token.cpu().numpy(), tok) and np.array_equal(value.cpu().numpy(), val), f"V {V}: greedy token"
+
+
+def test_layers_built_from_safetensors_shards(mlxq, oracle, tmp_path):
+    # a model directory written the way MLX writes it (nested names of a multimodal export, 2-byte tensors that leave
+    # the following ones off 16-byte boundaries) -> WeightStore on the GPU -> Linear by prefix -> matvec against the oracle
+    import json
+    import struct
+    weights = importlib.import_module("mlx-runner_b200.weights")
+    fxs = {"model.layers.0.self_attn.o_proj": oracle.QuantFixture(O=72, K=512, bits=4, gs=64, with_bias=True, seed=3),
+           "model.layers.0.mlp.down_proj": oracle.QuantFixture(O=40, K=1024, bits=6, gs=64, scale_type=oracle.BF16, seed=4)}
+    header, blobs, off = {}, [], 0
+
+    def put(name, dt, arr):
+        nonlocal off
+        b = np.ascontiguousarray(arr).tobytes()
+        header["language_model." + name] = {"dtype": dt, "shape": list(arr.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    put("model.layer_scalar", "F16", np.array([0.5], dtype=np.float16))                 # shifts everything after it
+    for prefix, fx in fxs.items():
+        sdt = "F16" if fx.scale_type == oracle.F16 else "BF16"
+        put(prefix + ".weight", "U32", fx.packed.view(np.uint32).reshape(fx.O, -1))
+        put(prefix + ".scales", sdt, fx.scales_raw)
+        put(prefix + ".biases", sdt, fx.biases_raw)
+        if fx.bias_raw is not None:
+            put(prefix + ".bias", sdt, fx.bias_raw)
+    text = json.dumps(header).encode()
+    text += b" " * (-len(text) % 8)
+    d = tmp_path / "model"
+    d.mkdir()
+    with open(d / "model.safetensors", "wb") as fh:
+        fh.write(struct.pack("<Q", len(text)) + text + b"".join(blobs))
+    store = weights.WeightStore(str(d), device=0)
+    assert store.totalBytes == off
+    for prefix, fx in fxs.items():
+        lin = store.linear(prefix, inDim=fx.K, outDim=fx.O)
+        assert (lin.bits, lin.groupSize, lin.outDim) == (fx.bits, fx.gs, fx.O)
+        for T in (1, 5):
+            x = oracle.RNG(T + fx.O).floats(T * fx.K).reshape(T, fx.K)
+            y = torch.zeros((T, fx.O), dtype=torch.float32, device="cuda")
+            lin.encode(None, as_dtype(x, 0), fx.K, y, fx.O, T)
+            torch.cuda.synchronize()
+            close(oracle, y.cpu().numpy(), fx.reference(x), f"{prefix} T {T}")
+    with pytest.raises(mlxq.InvalidFile):
+        store.linear("model.layers.0.mlp.down_proj", inDim=fxs["model.layers.0.mlp.down_proj"].K, outDim=41)
