@@ -211,6 +211,32 @@ class WeightStore:
             raise MissingTensor(prefix + ".biases")
         return self.require(prefix + ".weight"), s, b, self.get(prefix + ".bias")
 
+    def shardParts(self, prefix: str, rank: int, nranks: int, device=None):
+        """Rows [rank * O / nranks, (rank + 1) * O / nranks) of a layer's tensors, each slice copied to ``device`` on its
+        own -- with the store kept in host memory (``device=None`` at construction) a rank then holds 1 / nranks of the
+        layer in HBM instead of all of it.  The row count must divide evenly."""
+        import torch
+        w, s, b, bias = self.parts(prefix)
+        rows = int(w.shape[0])
+        if nranks < 1 or not 0 <= rank < nranks or rows % nranks != 0:
+            raise InvalidFile(f"{prefix}: {rows} rows do not split over {nranks} ranks")
+        r0, r1 = rank * (rows // nranks), (rank + 1) * (rows // nranks)
+        target = None if device is None else (torch.device("cuda", device) if isinstance(device, int) else torch.device(device))
+
+        def cut(t):
+            if t is None:
+                return None
+            if int(t.shape[0]) != rows:
+                raise InvalidFile(f"{prefix}: inconsistent quantization tensors")
+            piece = t[r0:r1].contiguous()
+            return piece if target is None else piece.to(target)
+        return cut(w), cut(s), cut(b), cut(bias)
+
+    def linearShard(self, prefix: str, inDim: int, rank: int, nranks: int, device: int) -> Linear:
+        """This rank's row shard of a layer, built from its slice alone (``Linear.shard(..., full=False)``)."""
+        w, s, b, bias = self.shardParts(prefix, rank, nranks, device)
+        return Linear.shard(w, s, b, bias, inDim=inDim, rank=rank, nranks=nranks, full=False, name=prefix, device=device)
+
     def linear(self, prefix: str, inDim: int, outDim: Optional[int] = None, device: Optional[int] = None) -> Linear:
         """``Linear(store, prefix, inDim:, outDim:)`` (``Transformer.swift:40-46``); the tensors must be on a GPU."""
         w, s, b, bias = self.parts(prefix)

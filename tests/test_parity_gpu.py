@@ -399,3 +399,14 @@ def test_layers_built_from_safetensors_shards(mlxq, oracle, tmp_path):
             close(oracle, y.cpu().numpy(), fx.reference(x), f"{prefix} T {T}")
     with pytest.raises(mlxq.InvalidFile):
         store.linear("model.layers.0.mlp.down_proj", inDim=fxs["model.layers.0.mlp.down_proj"].K, outDim=41)
+    # a rank's row shard built from its slice alone (the store stays in host memory, only the slice goes to the GPU)
+    host = weights.WeightStore(str(d))
+    prefix, fx = "model.layers.0.mlp.down_proj", fxs["model.layers.0.mlp.down_proj"]
+    x = oracle.RNG(77).floats(3 * fx.K).reshape(3, fx.K)
+    y = torch.zeros((3, fx.O), dtype=torch.float32, device="cuda")
+    for r in range(2):
+        shard = host.linearShard(prefix, fx.K, r, 2, device=0)
+        assert (shard.outDim, shard.totalOut, shard.rowOffset) == (fx.O // 2, fx.O, r * (fx.O // 2))
+        shard.encode(None, as_dtype(x, 0), fx.K, y[:, shard.rowOffset:], fx.O, 3)
+    torch.cuda.synchronize()
+    close(oracle, y.cpu().numpy(), fx.reference(x), "row shards from slices")

@@ -130,3 +130,66 @@ def test_store_uses_the_index_aliases_and_leaves_unused_tensors_on_disk(tmp_path
     empty.mkdir()
     with pytest.raises(mlxq.InvalidFile):
         weights.WeightStore(str(empty))
+
+
+def _write_raw(tmp_path, header: str, payload: bytes, header_len=None):
+    d = tmp_path / "m"
+    d.mkdir(exist_ok=True)
+    text = header.encode()
+    with open(d / "model.safetensors", "wb") as fh:
+        fh.write(struct.pack("<Q", len(text) if header_len is None else header_len) + text + payload)
+    return str(d)
+
+
+def test_reference_case_misaligned_tensor_is_realigned(tmp_path):
+    # Tests/MLXEngineTests/EngineTests.swift:126-152: a = 3 x f16 (6 bytes) so b starts misaligned; b = 4 x f32
+    a = np.array([1, 2, 3], dtype=np.float16)
+    b = np.array([0.5, -1, 2.25, 8], dtype=np.float32)
+    header = '{"a":{"dtype":"F16","shape":[3],"data_offsets":[0,6]},"b":{"dtype":"F32","shape":[4],"data_offsets":[6,22]}}'
+    while (len(header) + 8) % 8 != 0:
+        header += " "
+    store = weights.WeightStore(_write_raw(tmp_path, header, a.tobytes() + b.tobytes()))
+    tb = store.require("b")
+    assert tuple(tb.shape) == (4,) and str(tb.dtype) == "torch.float32"
+    assert tb.data_ptr() % 16 == 0
+    assert tb.numpy().tolist() == b.tolist()
+    assert store.get("missing") is None
+
+
+@pytest.mark.parametrize("header", [
+    '{"a":{"dtype":"F32","shape":[4],"data_offsets":[0,1000]}}',                    # past end of file
+    '{"a":{"dtype":"F32","shape":[4],"data_offsets":[8,0]}}',                       # start > end
+    '{"a":{"dtype":"F32","shape":[4],"data_offsets":[-16,0]}}',                     # negative
+    '{"a":{"dtype":"F32","shape":[5],"data_offsets":[0,16]}}',                      # shape / bytes mismatch
+    '{"a":{"dtype":"F32","shape":[4611686018427387904,4],"data_offsets":[0,16]}}',  # overflow
+    '{"a":{"dtype":"F32","shape":[-4],"data_offsets":[0,16]}}',                     # negative dim
+    "not json",
+])
+def test_reference_cases_malformed_headers(tmp_path, header):
+    # EngineTests.swift:166-179, the reference's own malformed headers, 16 bytes of payload
+    with pytest.raises(mlxq.EngineError):
+        weights.WeightStore(_write_raw(tmp_path, header, bytes(16)))
+
+
+def test_reference_case_huge_header_length(tmp_path):
+    # EngineTests.swift:181-190
+    with pytest.raises(mlxq.EngineError):
+        weights.WeightStore(_write_raw(tmp_path, "", bytes(64), header_len=2 ** 64 - 5))
+
+
+def test_a_rank_takes_only_its_rows(tmp_path):
+    g = np.random.default_rng(4)
+    d = tmp_path / "model"
+    d.mkdir()
+    layer = {f"model.layers.0.mlp.up_proj.{k}": v for k, v in quant_layer(g, 24, 128).items()}
+    layer["model.layers.0.mlp.up_proj.bias"] = ("F16", g.random(24).astype(np.float16))
+    write_safetensors(d / "model.safetensors", layer)
+    store = weights.WeightStore(str(d))                                   # host-resident
+    whole = store.parts("model.layers.0.mlp.up_proj")
+    got = [store.shardParts("model.layers.0.mlp.up_proj", r, 3) for r in range(3)]
+    import torch
+    for i, t in enumerate(whole):
+        assert torch.equal(torch.cat([p[i] for p in got]), t)
+        assert all(p[i].shape[0] == 8 and p[i].is_contiguous() for p in got)
+    with pytest.raises(mlxq.InvalidFile):
+        store.shardParts("model.layers.0.mlp.up_proj", 0, 5)              # 24 rows over 5 ranks
