@@ -163,6 +163,23 @@ MLXQ_API int mlxq_linear_lookup(mlxq_linear_t h, mlxq_stream_t stream, const int
 MLXQ_API int mlxq_linear_forward_rows(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, float* y,
                                       const uint32_t* count, const int32_t* list, int64_t max_rows);
 
+/* silu_mul / gelu_tanh_mul (Kernels.swift:2004-2030): out[t, i] = act(gu[t, i]) * gu[t, cols + i]; gu is fp32
+ * [T, stride] (the [gate | up] buffer of a fused gate/up projection), out fp32 [T, cols]. */
+MLXQ_API int mlxq_act_mul(mlxq_stream_t stream, int device, const float* gu, int64_t stride, int64_t cols, int64_t T, int act,
+                          float* out);
+
+/* The down projection reading the [gate | up] buffer itself (no counterpart in the reference, which runs silu_mul as a
+ * kernel of its own between the two projections, Transformer.swift:1528-1535): y = Linear(act(gu[:, :in_dim]) *
+ * gu[:, in_dim : 2 in_dim]), the product formed while the decode kernel stages its activations.  1 to 8 tokens, shapes
+ * the persistent decode kernels serve; others return MLXQ_UNSUPPORTED (use mlxq_act_mul, then mlxq_linear_forward). */
+MLXQ_API int mlxq_linear_forward_glu(mlxq_linear_t h, mlxq_stream_t stream, const float* gu, int64_t gu_stride, int act,
+                                     void* y, int y_dtype, int64_t y_stride, int64_t T);
+
+/* add_rms_norm (Kernels.swift:1141-1175): h += r; y = RMSNorm(h) * w, for `rows` rows of `dim` fp32 values `row_stride`
+ * apart (dim a multiple of 4, rows 16-byte aligned); w is [dim] in w_dtype. */
+MLXQ_API int mlxq_add_rms_norm(mlxq_stream_t stream, int device, float* h, const float* r, float* y, const void* w,
+                               int w_dtype, int64_t dim, int64_t rows, int64_t row_stride, float eps);
+
 /* First pass of the token selection (sample_blocks, Kernels.swift:2339-2377): for every token t and every block b of
  * 256 logits, the block's maximum and the lowest index that holds it.  logits is fp32 [T, stride] on `device`;
  * pairs receives the maxima as fp32 [T][nb] followed by the indices as int32 [T][nb], nb = ceil(V / 256)

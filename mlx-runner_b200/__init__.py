@@ -11,10 +11,10 @@ from . import _lib
 from ._lib import ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, BF16, F16, F32
 from .linear import (CollectiveFailure, Comm, DeviceTimeout, EngineError, GPUFailure, InvalidArgument, InvalidFile,
                      InvalidOutput, Linear, MissingTensor, OutOfMemory, SELECT_BLOCK, SELECT_NONE, TensorView, Unsupported,
-                     blockArgmax, blockMax, check, streamStatus)
+                     actMul, addRMSNorm, blockArgmax, blockMax, check, streamStatus)
 
 _lib.load()
 
 __all__ = ["Linear", "Comm", "TensorView", "EngineError", "InvalidFile", "Unsupported", "MissingTensor", "OutOfMemory",
            "GPUFailure", "InvalidArgument", "InvalidOutput", "CollectiveFailure", "DeviceTimeout", "check",
-           "streamStatus", "blockMax", "blockArgmax", "SELECT_BLOCK", "SELECT_NONE", "F32", "F16", "BF16", "ACT_SILU", "ACT_GELU_TANH", "ACT_GELU_ERF"]
+           "streamStatus", "blockMax", "blockArgmax", "actMul", "addRMSNorm", "SELECT_BLOCK", "SELECT_NONE", "F32", "F16", "BF16", "ACT_SILU", "ACT_GELU_TANH", "ACT_GELU_ERF"]

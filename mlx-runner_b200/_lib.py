@@ -62,6 +62,11 @@ SIGNATURES = {
     "mlxq_linear_forward_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                            C.c_void_p, C.c_int64]),
     "mlxq_unpack_codes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mlxq_act_mul": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "mlxq_linear_forward_glu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_int, C.c_int64,
+                                          C.c_int64]),
+    "mlxq_add_rms_norm": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
+                                    C.c_int64, C.c_int64, C.c_float]),
     "mlxq_block_max": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "mlxq_block_argmax": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "mlxq_fusable": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),

@@ -224,9 +224,11 @@ static size_t mma_plan(const mlxq_linear_t* parts, int n, int x_dtype, int64_t T
 
 static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const void* x, int x_dtype, int64_t x_stride,
                    void* y, int y_dtype, int64_t y_stride, int64_t T, const float* e, int act,
-                   const PeerGather* peer = nullptr) {
+                   const PeerGather* peer = nullptr, const float* x_up = nullptr, int x_act = 0) {
     QmvParams p;
     fill_qmv(p, parts, n);
+    p.x_up = x_up;
+    p.x_act = x_act;
     if (peer) p.peer = *peer; else p.peer.n = 0;
     p.x_dtype = x_dtype;
     p.y_dtype = y_dtype;
@@ -277,11 +279,13 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         if (persistent && !rsmem && T >= 4 && fits_persistent(h0) && fits_persistent(T - h0)) {
             // Too many staged activation columns for a CTA's shared memory (long rows): two calls of half the tokens,
             // each on a persistent kernel, beat the register-fed kernel although the weights are read twice.
-            const int rc = run_qmv(parts, n, st, x, x_dtype, x_stride, y, y_dtype, y_stride, h0, e, act, nullptr);
+            const int rc = run_qmv(parts, n, st, x, x_dtype, x_stride, y, y_dtype, y_stride, h0, e, act, nullptr, x_up, x_act);
             if (rc != MLXQ_OK) return rc;
             return run_qmv(parts, n, st, static_cast<const char*>(x) + static_cast<size_t>(h0) * x_stride * dtype_size(x_dtype), x_dtype, x_stride,
-                           static_cast<char*>(y) + static_cast<size_t>(h0) * y_stride * dtype_size(y_dtype), y_dtype, y_stride, T - h0, e, act, nullptr);
+                           static_cast<char*>(y) + static_cast<size_t>(h0) * y_stride * dtype_size(y_dtype), y_dtype, y_stride, T - h0, e, act, nullptr,
+                           x_up ? x_up + static_cast<size_t>(h0) * x_stride : nullptr, x_act);
         }
+        if (x_up && !rsmem) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernels: no gated input");
         if (rsmem || smem) {
             cudaError_t err = rsmem ? launch_qmv_pipe(parts[0]->bits, mp, pp, rsmem, parts[0]->device, st)
                                     : launch_qmv_mma(parts[0]->bits, mp, smem, parts[0]->device, st);
@@ -290,6 +294,7 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
         }
     }
     if (peer) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernel: no fused gather");
+    if (x_up) return fail(MLXQ_UNSUPPORTED, "this shape does not run on the persistent decode kernels: no gated input");
     // gridDim.y carries token tiles of four; walk very long batches in slices.
     const int64_t slice = 4 * 65535;
     for (int64_t t0 = 0; t0 < T; t0 += slice) {
@@ -578,6 +583,43 @@ int mlxq_linear_forward_gated(mlxq_linear_t h, mlxq_stream_t stream, const void*
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
     return run_qmv(&h, 1, static_cast<cudaStream_t>(stream), x, x_dtype, h->in_dim, y, y_dtype, h->out_dim, 1, e, act);
+}
+
+int mlxq_linear_forward_glu(mlxq_linear_t h, mlxq_stream_t stream, const float* gu, int64_t gu_stride, int act, void* y,
+                            int y_dtype, int64_t y_stride, int64_t T) {
+    if (!h || !gu) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (act < 0 || act > 2) return fail(MLXQ_INVALID_ARGUMENT, "act %d", act);
+    if (T < 1 || T > 8) return fail(MLXQ_UNSUPPORTED, "gated input serves 1 to 8 tokens (T = %lld)", (long long)T);
+    if (gu_stride < 2 * h->in_dim) return fail(MLXQ_INVALID_ARGUMENT, "gate|up stride %lld < 2 x in_dim", (long long)gu_stride);
+    if (int rc = check_x(gu, MLXQ_F32, gu_stride, h->in_dim, T)) return rc;
+    if (int rc = check_x(gu + h->in_dim, MLXQ_F32, gu_stride, h->in_dim, T)) return rc;
+    if (!y || !valid_dtype(y_dtype)) return fail(MLXQ_INVALID_ARGUMENT, "y is null or has dtype %d", y_dtype);
+    if (T > 1 && y_stride < h->out_dim) return fail(MLXQ_INVALID_ARGUMENT, "y stride %lld < out_dim", (long long)y_stride);
+    DeviceGuard guard(h->device);
+    if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
+    return run_qmv(&h, 1, static_cast<cudaStream_t>(stream), gu, MLXQ_F32, gu_stride, y, y_dtype, y_stride, T, nullptr, 0, nullptr,
+                   gu + h->in_dim, act);
+}
+
+int mlxq_act_mul(mlxq_stream_t stream, int device, const float* gu, int64_t stride, int64_t cols, int64_t T, int act, float* out) {
+    if (!gu || !out) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (act < 0 || act > 2 || cols < 1 || T < 0 || stride < 2 * cols) return fail(MLXQ_INVALID_ARGUMENT, "act %d, cols %lld, T %lld, stride %lld", act, (long long)cols, (long long)T, (long long)stride);
+    DeviceGuard guard(device);
+    if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", device);
+    cudaError_t err = launch_act_mul(gu, stride, cols, T, act, out, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? MLXQ_OK : cuda_fail(err, "act_mul launch");
+}
+
+int mlxq_add_rms_norm(mlxq_stream_t stream, int device, float* h, const float* r, float* y, const void* w, int w_dtype,
+                      int64_t dim, int64_t rows, int64_t row_stride, float eps) {
+    if (!h || !r || !y || !w) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (!valid_dtype(w_dtype) || dim < 4 || dim % 4 != 0 || rows < 0 || row_stride < dim || row_stride % 4 != 0)
+        return fail(MLXQ_INVALID_ARGUMENT, "dim %lld, rows %lld, row stride %lld, weight dtype %d", (long long)dim, (long long)rows, (long long)row_stride, w_dtype);
+    if (!aligned16(h) || !aligned16(r) || !aligned16(y)) return fail(MLXQ_INVALID_ARGUMENT, "rows must be 16-byte aligned");
+    DeviceGuard guard(device);
+    if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", device);
+    cudaError_t err = launch_add_rms_norm(h, r, y, w, w_dtype, dim, rows, row_stride, eps, static_cast<cudaStream_t>(stream));
+    return err == cudaSuccess ? MLXQ_OK : cuda_fail(err, "add_rms_norm launch");
 }
 
 int mlxq_linear_lookup(mlxq_linear_t h, mlxq_stream_t stream, const int32_t* ids, float* out, int64_t T) {

@@ -203,4 +203,61 @@ cudaError_t launch_block_argmax(const uint32_t* pairs, int n_seg, long long T, i
     return cudaGetLastError();
 }
 
+// ---- silu_mul / gelu_tanh_mul (Kernels.swift:2004-2030): out[t, i] = act(gu[t, i]) * gu[t, cols + i] ----------------
+__global__ void act_mul_kernel(const float* __restrict__ gu, long long stride, long long cols, int act, float* __restrict__ out) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long t = blockIdx.y;
+    if (i >= cols) return;
+    const float g = gu[t * stride + i], u = gu[t * stride + cols + i];
+    out[t * cols + i] = act_mul(act, g, u);
+}
+
+// ---- add_rms_norm (Kernels.swift:1141-1175): h += r; y = RMSNorm(h) * w, one CTA per row.  The sum of squares is
+// taken per thread over float4s in a strided order, then per warp, then over the warps in order, as the reference's
+// threadgroup does; dim is a multiple of 4 and the rows are 16-byte aligned (checked on the host). -------------------
+__global__ void add_rms_norm_kernel(float* __restrict__ hbuf, const float* __restrict__ r, float* __restrict__ y, const void* __restrict__ w,
+                                    int w_dtype, int dim, long long row_stride, float eps) {
+    __shared__ float buf[32];
+    const long long row = blockIdx.x;
+    float4* hr = reinterpret_cast<float4*>(hbuf + row * row_stride);
+    const float4* rr = reinterpret_cast<const float4*>(r + row * row_stride);
+    float4* yr = reinterpret_cast<float4*>(y + row * row_stride);
+    const int n4 = dim / 4;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        const float4 a = hr[i], b = rr[i];
+        const float4 v = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+        hr[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) buf[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int s = 0; s < nw; s++) tot += buf[s];
+    const float inv = rsqrtf(tot / static_cast<float>(dim) + eps);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        const float4 v = hr[i];
+        const float w0 = load_scalar(w, w_dtype, 4 * i), w1 = load_scalar(w, w_dtype, 4 * i + 1), w2 = load_scalar(w, w_dtype, 4 * i + 2),
+                    w3 = load_scalar(w, w_dtype, 4 * i + 3);
+        yr[i] = make_float4(v.x * inv * w0, v.y * inv * w1, v.z * inv * w2, v.w * inv * w3);
+    }
+}
+
+cudaError_t launch_act_mul(const float* gu, long long stride, long long cols, long long T, int act, float* out, cudaStream_t st) {
+    if (T == 0) return cudaSuccess;
+    if (T > 65535) return cudaErrorInvalidValue;
+    act_mul_kernel<<<dim3(static_cast<unsigned>((cols + 255) / 256), static_cast<unsigned>(T)), 256, 0, st>>>(gu, stride, cols, act, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_add_rms_norm(float* h, const float* r, float* y, const void* w, int w_dtype, long long dim, long long rows,
+                                long long row_stride, float eps, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    add_rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(h, r, y, w, w_dtype, static_cast<int>(dim), row_stride, eps);
+    return cudaGetLastError();
+}
+
 }  // namespace mlxq

@@ -20,4 +20,10 @@ cudaError_t launch_block_max(const float* logits, long long stride, long long V,
                              cudaStream_t st);
 cudaError_t launch_block_argmax(const uint32_t* pairs, int n_seg, long long T, int nb, int32_t* token, float* value, cudaStream_t st);
 
+// Elementwise neighbours of the projections: out[t, i] = act(gu[t, i]) * gu[t, cols + i], and the residual add fused with
+// the next RMS norm (h += r; y = RMSNorm(h) * w).
+cudaError_t launch_act_mul(const float* gu, long long stride, long long cols, long long T, int act, float* out, cudaStream_t st);
+cudaError_t launch_add_rms_norm(float* h, const float* r, float* y, const void* w, int w_dtype, long long dim, long long rows,
+                                long long row_stride, float eps, cudaStream_t st);
+
 }  // namespace mlxq

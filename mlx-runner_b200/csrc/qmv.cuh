@@ -42,6 +42,8 @@ struct QmvParams {
     int seg32;          // gs % 32 == 0: one (scale, bias) per aligned 32-code segment
     int gs_shift;       // log2(gs) when gs is a power of two, else -1
     PeerGather peer;    // sharded calls of the persistent decode kernel: peers that receive the rows too
+    const float* x_up;  // gated input (persistent kernels only): x is the fp32 gate half, x_up the up half, and the
+    int x_act;          // activations the layer sees are act(x) * x_up (silu_mul / gelu_*_mul folded into the staging)
 };
 
 template <int BITS> struct QmvUnit {

@@ -462,6 +462,13 @@ qmv_pipe_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ Pip
             } else if (idx < total_chunks) {
                 float v[8];
                 load8_coherent(q.x, q.x_dtype, static_cast<size_t>(tok) * q.x_stride + k, v);
+                if (q.x_up != nullptr) {
+                    // gated input: the activation the layer sees is act(gate) * up, formed here instead of by a kernel of its own
+                    float u[8];
+                    load8_coherent(q.x_up, DT_F32, static_cast<size_t>(tok) * q.x_stride + k, u);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) v[i] = act_mul(q.x_act, v[i], u[i]);
+                }
 #pragma unroll
                 for (int i = 0; i < 8; i++) sum += v[i];
                 if (split == 1) {

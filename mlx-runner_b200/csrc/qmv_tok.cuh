@@ -264,6 +264,13 @@ qmv_tok_kernel(const __grid_constant__ MmaParams p, const __grid_constant__ TokP
                 } else if (idx < total_chunks) {
                     float v[8];
                     raw_to_float8(q.x_dtype, ra[u], rb[u], v);
+                    if (q.x_up != nullptr) {
+                        // gated input: the activation the layer sees is act(gate) * up, formed here
+                        float up[8];
+                        load8_coherent(q.x_up, DT_F32, static_cast<size_t>(tok) * q.x_stride + k, up);
+#pragma unroll
+                        for (int i = 0; i < 8; i++) v[i] = act_mul(q.x_act, v[i], up[i]);
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; i++) sum += v[i];
                     if (split == 1) {

@@ -268,6 +268,12 @@ class Linear:
         check(L.load().mlxq_linear_forward_gated(self._h, _stream_handle(stream), _ptr(x), _act_dtype(x, xDtype), _ptr(y),
                                                  _act_dtype(y, yDtype), _ptr(e), act))
 
+    def encodeGLU(self, stream, gu, guStride: int, act: int, y, yStride: int, T: int, yDtype: Optional[int] = None) -> None:
+        """y = self(act(gu[:, :inDim]) * gu[:, inDim:2 inDim]): the down projection reading the fp32 [gate | up] buffer
+        itself, ``silu_mul`` (``Kernels.swift:2004-2013``) folded into the staging of its activations.  1-8 tokens."""
+        check(L.load().mlxq_linear_forward_glu(self._h, _stream_handle(stream), _ptr(gu), guStride, act, _ptr(y),
+                                               _act_dtype(y, yDtype), yStride, T))
+
     def encodeLookup(self, stream, ids, out, T: int) -> None:
         """out[t, :] = dequantised row ids[t] in fp32 (``Transformer.swift:318-344``)."""
         check(L.load().mlxq_linear_lookup(self._h, _stream_handle(stream), _ptr(ids), _ptr(out), T))
@@ -360,6 +366,18 @@ class Linear:
 
 SELECT_BLOCK = 256          # logits per block of the selection's first pass
 SELECT_NONE = 0x7FFFFFFF    # index reported for a block (or token) with no value above -inf
+
+
+def actMul(stream, gu, stride: int, cols: int, T: int, act: int, out, device: int = 0) -> None:
+    """out[t, i] = act(gu[t, i]) * gu[t, cols + i] (``silu_mul`` / ``gelu_tanh_mul``, ``Kernels.swift:2004-2030``)."""
+    check(L.load().mlxq_act_mul(_stream_handle(stream), device, _ptr(gu), stride, cols, T, act, _ptr(out)))
+
+
+def addRMSNorm(stream, h, r, y, w, dim: int, rows: int, rowStride: int, eps: float, wDtype: Optional[int] = None,
+               device: int = 0) -> None:
+    """h += r; y = RMSNorm(h) * w (``add_rms_norm``, ``Kernels.swift:1141-1175``)."""
+    check(L.load().mlxq_add_rms_norm(_stream_handle(stream), device, _ptr(h), _ptr(r), _ptr(y), _ptr(w), _act_dtype(w, wDtype),
+                                     dim, rows, rowStride, eps))
 
 
 def blockMax(stream, logits, V: int, T: int, stride: int, pairs, indexBase: int = 0, device: int = 0) -> None:

@@ -350,3 +350,12 @@ def block_argmax(bmax: np.ndarray, barg: np.ndarray):
                 best, bi = m, int(ix)
         tok[t], val[t] = bi, best
     return tok, val
+
+
+def add_rms_norm(h: np.ndarray, r: np.ndarray, w: np.ndarray, eps: float):
+    """``add_rms_norm`` (Sources/MLXEngine/Kernels.swift:1141-1175): h += r; y = RMSNorm(h) * w, row by row.  Returns
+    (h, y) in fp32; the sum of squares is accumulated in float64 here (the kernel's fp32 tree sits within 1e-6 of it)."""
+    h = (np.asarray(h, dtype=np.float32) + np.asarray(r, dtype=np.float32)).astype(np.float32)
+    ss = np.sum(h.astype(np.float64) ** 2, axis=-1, keepdims=True)
+    inv = (1.0 / np.sqrt(ss / h.shape[-1] + eps)).astype(np.float32)
+    return h, (h * inv * np.asarray(w, dtype=np.float32)).astype(np.float32)

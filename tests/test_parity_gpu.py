@@ -363,7 +363,7 @@ def test_layers_built_from_safetensors_shards(mlxq, oracle, tmp_path):
     import struct
     weights = importlib.import_module("mlx-runner_b200.weights")
     fxs = {"model.layers.0.self_attn.o_proj": oracle.QuantFixture(O=72, K=512, bits=4, gs=64, with_bias=True, seed=3),
-           "model.layers.0.mlp.down_proj": oracle.QuantFixture(O=40, K=1024, bits=6, gs=64, scale_type=oracle.BF16, seed=4)}
+           "model.layers.0.mlp.down_proj": oracle.QuantFixture(O=48, K=1024, bits=6, gs=64, scale_type=oracle.BF16, seed=4)}
     header, blobs, off = {}, [], 0
 
     def put(name, dt, arr):
@@ -410,3 +410,46 @@ def test_layers_built_from_safetensors_shards(mlxq, oracle, tmp_path):
         shard.encode(None, as_dtype(x, 0), fx.K, y[:, shard.rowOffset:], fx.O, 3)
     torch.cuda.synchronize()
     close(oracle, y.cpu().numpy(), fx.reference(x), "row shards from slices")
+
+
+def test_gate_up_product_folded_into_the_down_projection(mlxq, oracle):
+    # silu_mul / gelu_tanh_mul (Kernels.swift:2004-2030) as a kernel of its own, and folded into the staging of the down
+    # projection's activations: both against the oracle's act_mul followed by the layer's reference product
+    g = np.random.default_rng(21)
+    for bits, K, O in ((4, 1024, 72), (6, 512, 40), (8, 1536, 48)):
+        fx = oracle.QuantFixture(O=O, K=K, bits=bits, gs=64, seed=bits)
+        layer = DevLayer.from_fixture(mlxq, fx)
+        for T, act in ((1, 0), (4, 1), (8, 0)):
+            stride = 2 * K + 8
+            gu = (g.standard_normal((T, stride)) * 1.5).astype(np.float32)
+            gud = torch.from_numpy(gu).cuda()
+            xref = oracle.act_mul(act, gu[:, :K], gu[:, K:2 * K])
+            out = torch.zeros((T, K), dtype=torch.float32, device="cuda")
+            mlxq.actMul(None, gud, stride, K, T, act, out)
+            y = torch.full((T, O + 3), float("nan"), dtype=torch.float32, device="cuda")
+            layer.linear.encodeGLU(None, gud, stride, act, y, O + 3, T)
+            torch.cuda.synchronize()
+            mlxq.streamStatus(None, 0)
+            close(oracle, out.cpu().numpy(), xref, f"act_mul bits {bits} T {T} act {act}", 1e-5)
+            close(oracle, y.cpu().numpy()[:, :O], fx.reference(xref), f"gated input bits {bits} T {T} act {act}")
+            assert torch.isnan(y[:, O:]).all()
+    with pytest.raises(mlxq.Unsupported):
+        layer.linear.encodeGLU(None, gud, stride, 0, y, O + 3, 9)
+
+
+def test_residual_add_fused_with_the_next_norm(mlxq, oracle):
+    # add_rms_norm (Kernels.swift:1141-1175): h += r; y = RMSNorm(h) * w
+    g = np.random.default_rng(22)
+    for dim, rows, wdt in ((4096, 5, torch.bfloat16), (1000, 1, torch.float32), (64, 3, torch.float16)):
+        stride = dim + 4
+        h = g.standard_normal((rows, stride)).astype(np.float32)
+        r = g.standard_normal((rows, stride)).astype(np.float32)
+        w = torch.from_numpy(g.standard_normal(dim).astype(np.float32)).to(wdt)
+        hd, rd = torch.from_numpy(h).cuda(), torch.from_numpy(r).cuda()
+        yd = torch.zeros((rows, stride), dtype=torch.float32, device="cuda")
+        mlxq.addRMSNorm(None, hd, rd, yd, w.cuda(), dim, rows, stride, 1e-6)
+        torch.cuda.synchronize()
+        href, yref = oracle.add_rms_norm(h[:, :dim], r[:, :dim], w.float().numpy(), 1e-6)
+        assert np.array_equal(hd.cpu().numpy()[:, :dim], href)
+        assert np.array_equal(hd.cpu().numpy()[:, dim:], h[:, dim:])                    # the padding is not touched
+        close(oracle, yd.cpu().numpy()[:, :dim], yref, f"add_rms_norm dim {dim}", 1e-5)
