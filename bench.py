@@ -558,6 +558,13 @@ def run_ours(args):
                                   local, fused, y_dev, keep[-1], x_host[last[1]].float().numpy())
         except Exception as e:      # noqa: BLE001
             select = {"error": f"{type(e).__name__}: {str(e)[:120]}"}
+    glu = None
+    if args.config == "c4" and world == 1 and batch <= 8:
+        try:
+            downs = [lin for (lin, k, o) in distinct.values() if k == 12288]
+            glu = glu_probe(mlxq, torch, downs, 12288, batch, local)
+        except Exception as e:      # noqa: BLE001
+            glu = {"error": f"{type(e).__name__}: {str(e)[:120]}"}
     if rank == 0:
         probe = prefill_probe(mlxq, torch, device, peaks) if world == 1 and not args.no_prefill and args.config == "default" else {"available": False}
         cpu = cpu_sample(args, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
@@ -590,6 +597,8 @@ def run_ours(args):
             out["cpu_baseline"] = cpu
         if select is not None:
             out["select"] = select
+        if glu is not None:
+            out["glu"] = glu
         print(json.dumps(out), flush=True)
         if check.startswith("FAILED"):
             raise SystemExit(f"bench.py: {check}")
@@ -684,6 +693,53 @@ def select_probe(mlxq, torch, dist, comm, lin, x, K, batch, total, world, rank, 
             "gathered_bytes_per_step": {"logits": int(total * 4 * batch) if world > 1 else 0,
                                         "block_maxima": int(world * 2 * nb * 4 * batch) if world > 1 else 0},
             "note": "head call + selection per token step; one API call per launch, CUDA events around 32 steps"}
+
+
+def glu_probe(mlxq, torch, downs, K, batch, device_index):
+    """Config 4's MLP tail: the activation product as a kernel of its own followed by the down projection (the
+    reference's sequence, Transformer.swift:1528-1536) against the down projection that reads the [gate | up] buffer
+    itself.  Every down projection of the walk once per graph (distinct weights), fp32 activations, CUDA events
+    around ten replays."""
+    dev = torch.device("cuda", device_index)
+    O = downs[0].outDim
+    gu = torch.randn((batch, 2 * K), device=dev, dtype=torch.float32)
+    xbuf = torch.empty((batch, K), device=dev, dtype=torch.float32)
+    y = torch.empty((batch, O), device=dev, dtype=torch.float32)
+    y2 = torch.empty((batch, O), device=dev, dtype=torch.float32)
+
+    def separate():
+        st = torch.cuda.current_stream()
+        for lin in downs:
+            mlxq.actMul(st, gu, 2 * K, K, batch, 0, xbuf, device=device_index)
+            lin.encode(st, xbuf, K, y, O, batch)
+
+    def folded():
+        st = torch.cuda.current_stream()
+        for lin in downs:
+            lin.encodeGLU(st, gu, 2 * K, 0, y2, O, batch)
+
+    def timed_us(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (10 * len(downs))
+    us_sep, us_fold = timed_us(separate), timed_us(folded)
+    mlxq.streamStatus(None, device_index)
+    same = float((y - y2).abs().max()) <= 1e-4 * max(1.0, float(y.abs().max()))
+    return {"act_mul_then_down_us": us_sep, "down_with_gated_input_us": us_fold, "outputs_agree": bool(same),
+            "note": f"down projection {O}x{K} b4 g64, batch {batch}, fp32 activations; per layer, {len(downs)} layers per graph"}
 
 
 def run_sweep(args):
