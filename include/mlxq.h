@@ -58,7 +58,7 @@ typedef void* mlxq_stream_t; /* a cudaStream_t; NULL is the legacy default strea
  * bits and group size are derived from the shapes exactly as Transformer.swift:68-70 does:
  * bits = weight_cols*32/in_dim, group_size = in_dim/scales_cols. */
 typedef struct mlxq_linear_desc {
-    const void* weight;      /* u32 [weight_rows, weight_cols] */
+    const void* weight;      /* u32 [weight_rows, weight_cols]; dense layers: see `reserved` */
     const void* scales;      /* [scales_rows, scales_cols], may be NULL only together with biases == NULL (error) */
     const void* biases;      /* [biases_rows, biases_cols] */
     const void* bias;        /* optional per-output-row bias [bias_len]; NULL if absent */
@@ -71,7 +71,8 @@ typedef struct mlxq_linear_desc {
     int32_t scale_dtype;     /* mlxq_dtype of scales and biases */
     int32_t bias_dtype;      /* mlxq_dtype of bias */
     int32_t device;          /* CUDA device ordinal the pointers live on */
-    int32_t reserved;
+    int32_t reserved;        /* dense layers (scales == biases == NULL): 1 + mlxq_dtype of the weights, which are then
+                              * [weight_rows, weight_cols = in_dim] elements of that type; 0 otherwise */
     const char* name;        /* used in error text only (the reference's `name prefix`); may be NULL */
 } mlxq_linear_desc;
 

@@ -30,6 +30,7 @@ COMMON = ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcom
 # (source, object name, extra flags)
 UNITS = [("qmv_inst.cu", f"qmv_b{b}.o", [f"-DMLXQ_BITS={b}"]) for b in (2, 3, 4, 5, 6, 8)] + [
     ("aux_kernels.cu", "aux_kernels.o", []),
+    ("dense.cu", "dense.o", []),
     ("qmv_mma.cu", "qmv_mma.o", []),
     ("qmv_pipe.cu", "qmv_pipe.o", []),
     ("qmv_tok.cu", "qmv_tok.o", []),

@@ -17,6 +17,7 @@
 #include "qmv.cuh"
 #include "qmv_mma.cuh"
 #include "qmv_pipe.cuh"
+#include "dense.cuh"
 #include "qmv_tok.cuh"
 
 namespace mlxq {
@@ -102,8 +103,21 @@ static int validate_desc(const mlxq_linear_desc* d, int* bits_out, int* gs_out) 
     if (d->bias && d->bias_len != d->weight_rows)
         return fail(MLXQ_INVALID_FILE, "%s: bias shape [%lld]", name, (long long)d->bias_len);
     if (d->scales && !d->biases) return fail(MLXQ_MISSING_TENSOR, "%s.biases", name);
-    if (!d->scales)
-        return fail(MLXQ_UNSUPPORTED, "%s: dense (unquantized) weights are outside this library", name);
+    if (!d->scales) {
+        // dense layer (Transformer.swift:103-112): weights of a floating type, as many columns as inputs
+        const int wdt = d->reserved - 1;
+        if (d->biases) return fail(MLXQ_INVALID_FILE, "%s: inconsistent quantization tensors", name);
+        if (!valid_dtype(wdt)) return fail(MLXQ_UNSUPPORTED, "%s: weight dtype of a dense layer not given or not floating", name);
+        if (d->weight_cols != d->in_dim)
+            return fail(MLXQ_INVALID_FILE, "%s: expected %lld input columns, found %lld", name, (long long)d->in_dim, (long long)d->weight_cols);
+        if (d->in_dim % 4 != 0) return fail(MLXQ_UNSUPPORTED, "%s: input dim %lld", name, (long long)d->in_dim);
+        if (d->bias && !valid_dtype(d->bias_dtype)) return fail(MLXQ_UNSUPPORTED, "%s: bias dtype %d", name, d->bias_dtype);
+        if (d->in_dim > (1LL << 30) || d->weight_rows > (1LL << 30)) return fail(MLXQ_UNSUPPORTED, "%s: dimensions beyond 2^30", name);
+        if (d->device < 0 || d->device >= 64) return fail(MLXQ_INVALID_ARGUMENT, "%s: device %d", name, d->device);
+        *bits_out = 0;
+        *gs_out = 0;
+        return MLXQ_OK;
+    }
     if (d->scales_rows != d->weight_rows || d->scales_cols <= 0 || d->in_dim % d->scales_cols != 0 ||
         d->biases_rows != d->scales_rows || d->biases_cols != d->scales_cols ||
         (d->weight_cols * 32) % d->in_dim != 0)
@@ -135,6 +149,7 @@ static mlxq_linear* make_handle(const mlxq_linear_desc* d, int bits, int gs) {
     h->gs = gs;
     h->s_dtype = d->scale_dtype;
     h->bias_dtype = d->bias ? d->bias_dtype : d->scale_dtype;
+    h->w_dtype = bits == 0 ? d->reserved - 1 : 0;
     h->device = d->device;
     h->row_offset = 0;
     h->total_out = d->weight_rows;
@@ -144,7 +159,7 @@ static mlxq_linear* make_handle(const mlxq_linear_desc* d, int bits, int gs) {
     // The reference resolves its fused decode kernel only under these conditions (Transformer.swift:76-77);
     // fusable() and canFuse() report them unchanged.
     const int align = bits == 4 ? 32 : 16;
-    h->qmv_eligible = d->in_dim % align == 0 && gs % align == 0 && (!d->bias || h->bias_dtype == h->s_dtype);
+    h->qmv_eligible = bits != 0 && d->in_dim % align == 0 && gs % align == 0 && (!d->bias || h->bias_dtype == h->s_dtype);
     return h;
 }
 
@@ -225,6 +240,8 @@ static size_t mma_plan(const mlxq_linear_t* parts, int n, int x_dtype, int64_t T
 static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const void* x, int x_dtype, int64_t x_stride,
                    void* y, int y_dtype, int64_t y_stride, int64_t T, const float* e, int act,
                    const PeerGather* peer = nullptr, const float* x_up = nullptr, int x_act = 0) {
+    for (int i = 0; i < n; i++)
+        if (parts[i]->bits == 0) return fail(MLXQ_UNSUPPORTED, "%s is a dense layer: only mlxq_linear_forward serves it", parts[i]->name.c_str());
     QmvParams p;
     fill_qmv(p, parts, n);
     p.x_up = x_up;
@@ -356,6 +373,12 @@ int forward_impl(mlxq_linear_t h, cudaStream_t st, const void* x, int x_dtype, i
     if (T > 1 && y_stride < h->out_dim) return fail(MLXQ_INVALID_ARGUMENT, "y stride %lld < out_dim", (long long)y_stride);
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
+    if (h->bits == 0) {
+        if (peer) return fail(MLXQ_UNSUPPORTED, "%s is a dense layer: no fused gather", h->name.c_str());
+        const cudaError_t err = launch_dense(h->w, h->w_dtype, h->bias, h->bias_dtype, x, x_dtype, x_stride, y, y_dtype, y_stride, T,
+                                             static_cast<int>(h->out_dim), static_cast<int>(h->in_dim), st);
+        return err == cudaSuccess ? MLXQ_OK : cuda_fail(err, "dense launch");
+    }
     if (gemm_tile_for(h, x_dtype, x_stride, x, T) > 0) {
         if (peer) return fail(MLXQ_UNSUPPORTED, "batches of %lld tokens take the GEMM: no fused gather", (long long)T);
         GemmCall c;
@@ -413,6 +436,7 @@ int mlxq_linear_create_shard(const mlxq_linear_desc* desc, int rank, int nranks,
     if (nranks < 1 || rank < 0 || rank >= nranks) return fail(MLXQ_INVALID_ARGUMENT, "rank %d of %d", rank, nranks);
     int bits = 0, gs = 0;
     if (int rc = validate_desc(desc, &bits, &gs)) return rc;
+    if (bits == 0) return fail(MLXQ_UNSUPPORTED, "%s: dense layers are not sharded", desc->name ? desc->name : "linear");
     mlxq_linear_desc d = *desc;
     int64_t total = desc->weight_rows;
     if (desc_is_full) {
@@ -454,6 +478,7 @@ void mlxq_linear_destroy(mlxq_linear_t h) {
 
 int mlxq_linear_prepare(mlxq_linear_t h, mlxq_stream_t stream) {
     if (!h) return fail(MLXQ_INVALID_ARGUMENT, "null layer");
+    if (h->bits == 0) return MLXQ_OK;
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
     if (qgemm_tile_tokens(gemm_layer(h), MLXQ_BF16, h->in_dim, nullptr, 1024) == 0) return MLXQ_OK;      // the GEMM never takes this layer
@@ -478,6 +503,7 @@ int mlxq_linear_forward(mlxq_linear_t h, mlxq_stream_t stream, const void* x, in
 int mlxq_linear_forward_static(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, int64_t x_stride, void* y,
                                int y_dtype, int64_t y_stride, int64_t T) {
     if (!h) return fail(MLXQ_INVALID_ARGUMENT, "null layer");
+    if (h->bits == 0) return fail(MLXQ_UNSUPPORTED, "%s is a dense layer: only mlxq_linear_forward serves it", h->name.c_str());
     if (T < 1) return fail(MLXQ_INVALID_ARGUMENT, "T = %lld", (long long)T);
     if (int rc = check_x(x, x_dtype, x_stride, h->in_dim, T)) return rc;
     if (!y || !valid_dtype(y_dtype)) return fail(MLXQ_INVALID_ARGUMENT, "y is null or has dtype %d", y_dtype);
@@ -538,13 +564,14 @@ int mlxq_use_gemm64(int64_t T, int64_t out_dim) {
 }
 
 int mlxq_gemm_tile_tokens(mlxq_linear_t h, int64_t T) {
-    if (!h || T < 1) return 0;
+    if (!h || T < 1 || h->bits == 0) return 0;
     return gemm_tile_for(h, MLXQ_BF16, h->in_dim, nullptr, T);
 }
 
 const char* mlxq_kernel_for(mlxq_linear_t h, int x_dtype, int y_dtype, int64_t T) {
     (void)y_dtype;
     if (!h || T < 1) return "";
+    if (h->bits == 0) return "dmm";
     if (gemm_tile_for(h, x_dtype, h->in_dim, nullptr, T) > 0) return "qgemm";
     return T <= 16 ? "qmv" : "qmm";
 }
@@ -624,6 +651,7 @@ int mlxq_add_rms_norm(mlxq_stream_t stream, int device, float* h, const float* r
 
 int mlxq_linear_lookup(mlxq_linear_t h, mlxq_stream_t stream, const int32_t* ids, float* out, int64_t T) {
     if (!h || !ids || !out) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (h->bits == 0) return fail(MLXQ_UNSUPPORTED, "%s is a dense layer: only mlxq_linear_forward serves it", h->name.c_str());
     if (T < 0) return fail(MLXQ_INVALID_ARGUMENT, "T = %lld", (long long)T);
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
@@ -638,6 +666,7 @@ int mlxq_linear_lookup(mlxq_linear_t h, mlxq_stream_t stream, const int32_t* ids
 int mlxq_linear_forward_rows(mlxq_linear_t h, mlxq_stream_t stream, const void* x, int x_dtype, float* y,
                              const uint32_t* count, const int32_t* list, int64_t max_rows) {
     if (!h || !x || !y || !count || !list) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (h->bits == 0) return fail(MLXQ_UNSUPPORTED, "%s is a dense layer: only mlxq_linear_forward serves it", h->name.c_str());
     if (!valid_dtype(x_dtype) || max_rows < 0) return fail(MLXQ_INVALID_ARGUMENT, "x dtype %d, max_rows %lld", x_dtype, (long long)max_rows);
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);
@@ -670,6 +699,7 @@ int mlxq_block_argmax(mlxq_stream_t stream, int device, const uint32_t* pairs, i
 
 int mlxq_unpack_codes(mlxq_linear_t h, mlxq_stream_t stream, uint8_t* out) {
     if (!h || !out) return fail(MLXQ_INVALID_ARGUMENT, "null argument");
+    if (h->bits == 0) return fail(MLXQ_UNSUPPORTED, "%s is a dense layer: only mlxq_linear_forward serves it", h->name.c_str());
     if (reinterpret_cast<uintptr_t>(out) % 8 != 0) return fail(MLXQ_INVALID_ARGUMENT, "out must be 8-byte aligned");
     DeviceGuard guard(h->device);
     if (!guard.ok()) return fail(MLXQ_GPU_FAILURE, "cannot select device %d", h->device);

@@ -16,7 +16,8 @@ struct mlxq_linear {
     const void* b;
     const void* bias;
     int64_t in_dim, out_dim;
-    int bits, gs;
+    int bits, gs;         // bits == 0: a dense (unquantized) layer, its weights in w_dtype
+    int w_dtype = 0;
     int s_dtype, bias_dtype;
     int device;
     int64_t row_offset;   // first global output row (shards)

@@ -178,6 +178,10 @@ class Linear:
         if w.dtype != "u32" and len(w.shape) == 2:
             # the reference takes any integer storage and counts bytes (Transformer.swift:57, :68)
             d.weight_cols = w.shape[1] * _DTYPE_SIZE[w.dtype] // 4 if (w.shape[1] * _DTYPE_SIZE[w.dtype]) % 4 == 0 else 0
+        if s is None and b is None and len(w.shape) == 2 and w.dtype in _DTYPE_CODE:
+            # a dense layer (Transformer.swift:103-112): the weights' own type travels in the descriptor's spare field
+            d.weight_cols = w.shape[1]
+            d.reserved = 1 + _DTYPE_CODE[w.dtype]
         d.scales = s.ptr if s else None
         d.biases = b.ptr if b else None
         d.scales_rows, d.scales_cols = (s.shape if s is not None and len(s.shape) == 2 else (0, 0))
@@ -215,7 +219,7 @@ class Linear:
         self.groupSize = int(lib.mlxq_linear_group_size(h))
         self.rowOffset = int(lib.mlxq_linear_row_offset(h))
         self.totalOut = int(lib.mlxq_linear_total_rows(h))
-        self.description = f"q{self.bits}g{self.groupSize}"
+        self.description = f"q{self.bits}g{self.groupSize}" if self.bits else w.dtype
 
     @classmethod
     def shard(cls, weight, scales, biases, bias=None, inDim: int = 0, rank: int = 0, nranks: int = 1, full: bool = True,

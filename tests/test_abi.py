@@ -68,8 +68,17 @@ def test_construction_errors_mirror_linear_init(mlxq):
         mlxq.Linear(tv(0x1000, "u32", (40, 7 * 512 // 32)), s, b, None, inDim=512)
     with pytest.raises(mlxq.Unsupported, match="group 4"):        # group size not a multiple of 8
         mlxq.Linear(w, tv(0x2000, "f16", (40, 128)), tv(0x3000, "f16", (40, 128)), None, inDim=512)
-    with pytest.raises(mlxq.Unsupported):                          # dense weights are outside this library
-        mlxq.Linear(tv(0x1000, "f16", (40, 512)), None, None, None, inDim=512)
+    # dense layers (Transformer.swift:103-112): a floating weight with as many columns as inputs, inDim % 4 == 0
+    dense = mlxq.Linear(tv(0x1000, "f16", (40, 512)), None, None, None, inDim=512)
+    assert (dense.bits, dense.outDim, dense.inDim, dense.description, dense.kernelFor(1)) == (0, 40, 512, "f16", "dmm")
+    with pytest.raises(mlxq.InvalidFile, match="expected 520 input columns"):
+        mlxq.Linear(tv(0x1000, "f16", (40, 512)), None, None, None, inDim=520)
+    with pytest.raises(mlxq.Unsupported, match="input dim"):
+        mlxq.Linear(tv(0x1000, "bf16", (40, 510)), None, None, None, inDim=510)
+    with pytest.raises(mlxq.Unsupported):                          # an integer tensor without scales is not a layer
+        mlxq.Linear(tv(0x1000, "u32", (40, 512)), None, None, None, inDim=512)
+    with pytest.raises(mlxq.Unsupported, match="not sharded"):
+        mlxq.Linear.shard(tv(0x1000, "f16", (40, 512)), None, None, None, inDim=512, rank=0, nranks=2)
     ok = mlxq.Linear(w, s, b, tv(0x4000, "f16", (40,)), inDim=512, outDim=40)
     assert ok.outDim == 40
 

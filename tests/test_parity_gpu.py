@@ -453,3 +453,28 @@ def test_residual_add_fused_with_the_next_norm(mlxq, oracle):
         assert np.array_equal(hd.cpu().numpy()[:, :dim], href)
         assert np.array_equal(hd.cpu().numpy()[:, dim:], h[:, dim:])                    # the padding is not touched
         close(oracle, yd.cpu().numpy()[:, :dim], yref, f"add_rms_norm dim {dim}", 1e-5)
+
+
+@pytest.mark.parametrize("wdt", [torch.float16, torch.bfloat16, torch.float32])
+def test_dense_layers_through_the_same_handle(mlxq, oracle, wdt):
+    # dmm (Kernels.swift:938-999): y = x . W^T + bias with W in f32 / f16 / bf16, fp32 accumulation; vector and scalar
+    # paths (a K that is not a multiple of 8, strided activations), batches beyond one pass of eight tokens
+    g = np.random.default_rng(31)
+    for O, K, T, xdt in ((72, 1024, 1, 1), (40, 1000, 5, 0), (33, 36, 20, 2), (16, 4096, 9, 1)):
+        w = torch.from_numpy((g.standard_normal((O, K)) * 0.05).astype(np.float32)).to(wdt).cuda()
+        bias = torch.from_numpy(g.standard_normal(O).astype(np.float32)).to(wdt).cuda() if O % 2 == 0 else None
+        lin = mlxq.Linear(w, None, None, bias, inDim=K, name="dense")
+        assert lin.bits == 0
+        x = g.standard_normal((T, K)).astype(np.float32)
+        xd = as_dtype(x, xdt)
+        pad = 8 if K % 8 == 0 else 4                                   # (activation rows stay 16-byte aligned)
+        xs = torch.zeros((T, K + pad), dtype=xd.dtype, device="cuda")
+        xs[:, :K] = xd
+        y = torch.full((T, O + 1), float("nan"), dtype=torch.float32, device="cuda")
+        lin.encode(None, xs, K + pad, y, O + 1, T)
+        torch.cuda.synchronize()
+        ref = oracle.matmul_dense(w.float().cpu().numpy(), xd.float().cpu().numpy(), None if bias is None else bias.float().cpu().numpy())
+        close(oracle, y.cpu().numpy()[:, :O], ref, f"dense {wdt} {O}x{K} T {T}", 2e-5)
+        assert torch.isnan(y[:, O]).all()
+        with pytest.raises(mlxq.Unsupported):
+            lin.unpackCodes(None, torch.zeros((O, K), dtype=torch.uint8, device="cuda"))
