@@ -239,8 +239,9 @@ MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_str
                                         int x_dtype, int64_t x_stride, float* y, int64_t y_stride, int64_t T);
 
 /* Fused shard forward + gather (no counterpart in the reference, which runs on one GPU).  The decode kernel
- * itself stores every output row into the gather window of every rank (peer memory over NVLink) and raises
- * a flag on every rank when its rows are out, so no collective kernel follows it.
+ * itself stores every output row into the gather window of every rank (peer memory over NVLink); the rank's next
+ * kernel on the communicator (the next fused call or mlxq_comm_wait) tells the peers that the rows are out, so no
+ * collective kernel follows the call.
  *
  * mlxq_comm_window allocates the window: two buffers of `bytes` each (a positive multiple of 256; at least
  * T * total rows * 4), mapped into the other ranks through CUDA IPC.  It is a collective: every rank calls
@@ -248,9 +249,9 @@ MLXQ_API int mlxq_linear_forward_gather(mlxq_linear_t h, mlxq_comm_t c, mlxq_str
  *
  * mlxq_linear_forward_gather_fused enqueues the call and returns in *y_full the device address of the
  * gathered output, fp32 [T, total rows] (row stride = total rows).  The kernel does not wait for the other
- * ranks: the rows are complete in `stream` order once the next fused call of the communicator has begun
- * (it waits for the peers before it reads its activations, while its weight copies are already in flight)
- * or after mlxq_comm_wait(c, stream), which enqueues that wait alone; any other reader needs the latter.
+ * ranks.  Their rows are complete for two readers only: the next fused call of the communicator when its x lies
+ * inside the window (it waits for the peers itself before it reads its activations, while its weight copies are
+ * already in flight), and anything enqueued after mlxq_comm_wait(c, stream), which enqueues that wait alone.
  * The rows may be read by work enqueued on `stream` before this rank's NEXT fused call on the communicator, and only
  * by such work: calls alternate between two buffers, and a peer that runs ahead starts storing its second-next
  * call's rows into this buffer as soon as this rank's next call has started.
