@@ -253,6 +253,35 @@ static int run_qmv(const mlxq_linear_t* parts, int n, cudaStream_t st, const voi
     p.y_stride = y_stride;
     p.e = e;
     p.act = act;
+    if (T > 16 && !peer && !x_up && !e) {
+        // A long batch on a layer the tensor-core GEMM does not take (anything but 4-bit, or unaligned): sixteen (or
+        // eight) tokens at a time on the token-major kernel -- the weights are then read once per sixteen tokens through
+        // the tensor cores instead of once per four through the CUDA cores.
+        for (int chunk = 16; chunk >= 8; chunk /= 2) {
+            MmaParams mc;
+            bool okc = false;
+            mma_plan(parts, n, x_dtype, chunk, mc, &okc);
+            if (!okc) continue;
+            p.T = chunk; p.x = x; p.y = y;
+            mc.q = p;
+            mc.err = device_error_word(parts[0]->device);
+            TokPlan tc;
+            const char* mode = getenv("MLXQ_DECODE");
+            if (!mc.err || (mode && (strcmp(mode, "mma") == 0 || strcmp(mode, "pipe") == 0)) ||
+                !qmv_tok_plan(parts[0]->bits, mc, chunk, device_sm_count(parts[0]->device), tc))
+                continue;
+            // (every call takes exactly `chunk` tokens -- the last one reaches back over tokens already done -- so a token's
+            // result does not depend on the batch it came in)
+            for (int64_t t0 = 0; t0 < T; t0 += chunk) {
+                const int64_t at = t0 + chunk <= T ? t0 : T - chunk;
+                const int rc = run_qmv(parts, n, st, static_cast<const char*>(x) + static_cast<size_t>(at) * x_stride * dtype_size(x_dtype), x_dtype,
+                                       x_stride, static_cast<char*>(y) + static_cast<size_t>(at) * y_stride * dtype_size(y_dtype), y_dtype, y_stride,
+                                       chunk, nullptr, act, nullptr);
+                if (rc != MLXQ_OK) return rc;
+            }
+            return MLXQ_OK;
+        }
+    }
     MmaParams mp;
     bool planned = false;
     const size_t smem = mma_plan(parts, n, x_dtype, T, mp, &planned);
