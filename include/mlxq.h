@@ -88,7 +88,10 @@ MLXQ_API const char* mlxq_last_error(void);
 /* ---- construction: Linear.init, Transformer.swift:48-111 ------------------------------------------- */
 
 /* Validates the description (shape rules of Transformer.swift:52-60, format rules of :68-73) and returns
- * a handle.  Nothing is copied.  Errors: MLXQ_INVALID_FILE, MLXQ_UNSUPPORTED, MLXQ_MISSING_TENSOR. */
+ * a handle.  Nothing is copied.  Errors: MLXQ_INVALID_FILE, MLXQ_UNSUPPORTED, MLXQ_MISSING_TENSOR.
+ * A description without scales and biases is a dense layer (Transformer.swift:103-112: floating weights,
+ * weight_cols == in_dim, in_dim a multiple of 4, the weights' type in `reserved`); mlxq_linear_forward serves it,
+ * the other entry points return MLXQ_UNSUPPORTED for such a handle, and it cannot be sharded. */
 MLXQ_API int mlxq_linear_create(const mlxq_linear_desc* desc, mlxq_linear_t* out);
 /* The same layer restricted to output rows [rank*out_dim/nranks, (rank+1)*out_dim/nranks): the row
  * sharding of large projections across GPUs.  `desc` holds either the full tensors (desc_is_full != 0:
