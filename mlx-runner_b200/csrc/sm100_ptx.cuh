@@ -59,7 +59,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* a
 }
 
 // Whole-warp wait for code that goes on to a ".sync.aligned" instruction (tcgen05.ld / tcgen05.st / mma.sync).
-// Lane 0 polls alone (bounded, like mbar_wait) and the verdict is broadcast; __syncwarp orders the other lanes'
+// Lane 0 polls alone (bounded, like mbar_wait) and the result is broadcast; __syncwarp orders the other lanes'
 // later reads after lane 0's acquire.  Must be called by all 32 lanes.
 //
 // Why one lane.  With every lane running its own mbar_wait before a tcgen05.st, the store now and then lost the
